@@ -1,0 +1,93 @@
+"""The CPU oracle replays the outputs of the executed reference (tests/golden/*.npz, made by
+tests/golden/make_golden.py).  fp32 tolerance: the oracle and the reference do the same fp32
+arithmetic in the same merge order, so they agree to rounding (<= 2e-5 abs)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ring_oracle as O
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")))
+TOL = 2e-5
+
+
+def _load(name):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    world, B, S, H, D, seed, rs = (int(x) for x in z["meta"])
+    return z, world, B, S, H, D, seed, rs
+
+
+def test_all_fixtures_present():
+    assert set(CASES) >= {"cfg1_n2", "trace_n4", "batch2_n4", "n8", "varlen_n4"}
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_matches_executed_reference(name):
+    z, world, B, S, H, D, seed, rs = _load(name)
+    div = z["dividers"].tolist()
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    cu = z["cu"].tolist() if "cu" in z.files else None
+    outs, states = O.run_ring_group(world, div, data, cu_per_rank=cu)
+    gold = z["out"]                                       # [T, world, B, S_loc/rs, H, D]
+    for t in range(len(div)):
+        for r in range(world):
+            mine = outs[t][r]
+            if cu is not None:
+                mine = mine[None]
+                valid = cu[r][1]                           # rows of the valid segment only: the
+                g = torch.from_numpy(gold[t, r])[:, :valid]  # reference leaves pad rows undefined
+                m = mine[:, :valid]
+            else:
+                g = torch.from_numpy(gold[t, r])
+                m = mine[:, ::rs]
+            assert m.shape == g.shape
+            err = (m - g).abs().max().item()
+            assert err <= TOL, f"{name} step {t} rank {r}: max-abs {err}"
+            if cu is None:
+                cs = mine.double().sum().item()
+                assert abs(cs - z["checksum"][t, r]) <= 1e-6 * max(1.0, z["abs_checksum"][t, r])
+
+
+def test_state_machine_events_match_reference_trace():
+    """Cache gets / puts of rank 1 for dividers 1,4,4,2,2,2,1 on four ranks, as logged from the
+    executed reference (its proCache.get_block / store_block calls)."""
+    z, world, B, S, H, D, seed, rs = _load("trace_n4")
+    div = z["dividers"].tolist()
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    _, states = O.run_ring_group(world, div, data)
+    mine = []
+    for e in states[1].log:
+        if e[0] == "put":
+            mine.append([0, e[1], e[2], 0])
+        elif e[0] == "get":
+            mine.append([1, e[1], e[2], int(e[3])])
+    assert mine == z["events_rank1"].tolist()
+
+
+def test_full_refresh_steps_equal_full_attention():
+    z, world, B, S, H, D, seed, rs = _load("trace_n4")
+    div = z["dividers"].tolist()
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    outs, _ = O.run_ring_group(world, div, data)
+    for t, d in enumerate(div):
+        if d != 1:
+            continue
+        q, k, v = data[t]
+        full, _ = O.partial_attention(q, k, v)
+        got = torch.cat(outs[t], dim=1)
+        assert (got - full).abs().max().item() < 5e-6
+
+
+def test_block_level_variant_equals_reference_on_screened_schedules():
+    z, world, B, S, H, D, seed, rs = _load("n8")
+    div = z["dividers"].tolist()
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    a, _ = O.run_ring_group(world, div, data)
+    b, _ = O.run_ring_group(world, div, data, block_level_first_kv=True)
+    for t in range(len(div)):
+        for r in range(world):
+            assert torch.equal(a[t][r], b[t][r])
