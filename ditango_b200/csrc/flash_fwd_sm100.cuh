@@ -1,0 +1,31 @@
+// Parameters and launcher of the partial-attention forward kernel (flash_fwd_sm100.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dtb {
+
+struct FlashParams {
+  void* out;               // fp32 or bf16, token stride out_tok_stride, head h at h*D
+  float* lse;              // fp32, natural log
+  const int32_t* cu_q;     // device cumulative offsets (packed batch) or nullptr (dense batch)
+  const int32_t* cu_k;
+  int* status;             // device status word (0 = ok)
+  int64_t out_tok_stride;  // elements
+  int64_t total_q;         // tokens behind q
+  int nseg;                // sequences (dense: batch size)
+  int seqlen_q;            // dense: exact; packed: upper bound per segment
+  int seqlen_k;
+  int num_heads;
+  float scale_log2;        // softmax_scale * log2(e)
+  int out_dtype;           // 0 fp32, 1 bf16
+  int lse_layout;          // 0 [B,H,S] (packed: [H,T]), 1 [B,S,H]
+  int accumulate;          // merge into the state already in (out, lse)
+};
+
+template <int D>
+cudaError_t launch_flash(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
+                         const FlashParams& p, cudaStream_t stream);
+
+}  // namespace dtb

@@ -1,0 +1,130 @@
+/*
+ * ditango_b200 -- C ABI of the sm_100a kernels behind DiTango's sequence-parallel attention path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*), launches asynchronously on that stream and returns an int
+ * status: 0 = launched; negative = rejected argument (nothing was launched, text in
+ * dtb_last_error()).  Pointers are borrowed: the caller keeps the memory alive until the
+ * stream has passed the call.  Nothing here allocates device memory.  The calling thread's
+ * current CUDA device must be the one that owns the pointers.
+ *
+ * Citations name the reference call site each entry point replaces (paths relative to the
+ * reference project root).
+ */
+#ifndef DITANGO_B200_H_
+#define DITANGO_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DTB_API __attribute__((visibility("default")))
+#else
+#define DTB_API
+#endif
+
+#define DTB_OK 0
+#define DTB_ERR_ARG (-1)      /* unsupported shape / null pointer / misaligned pointer          */
+#define DTB_ERR_CUDA (-2)     /* a CUDA runtime or driver call failed (launch, tensor map, ...) */
+#define DTB_ERR_DEVICE (-3)   /* current device is not compute capability 10.x                  */
+
+/* element types of partial-state outputs */
+#define DTB_F32 0
+#define DTB_BF16 1
+
+/* layouts of a log-sum-exp tensor that belongs to tokens [B,S] x heads H
+ * (packed inputs: B = 1, S = total tokens) */
+#define DTB_LSE_BHS 0         /* [B, H, S]  -- what flash_attn returns                         */
+#define DTB_LSE_BSH 1         /* [B, S, H]  -- the merged state's [B,S,H,1]                    */
+
+#define DTB_MERGE_MAX_STATES 16
+
+DTB_API int dtb_version(void);
+
+/* Text of the last rejected call on this host thread ("" if none). */
+DTB_API const char* dtb_last_error(void);
+
+/* 0 if the current device can run these kernels (compute capability 10.x), else DTB_ERR_DEVICE. */
+DTB_API int dtb_device_supported(void);
+
+/*
+ * Device-side status word.  Kernels that wait on hardware barriers bound every wait; a wait that
+ * runs out records a non-zero code and the kernel returns without storing results.
+ * dtb_read_status synchronises `stream`, returns the word (0 = all kernels completed normally)
+ * and clears it.
+ */
+DTB_API int dtb_read_status(void* stream);
+
+/*
+ * Partial attention state of a query chunk against ONE key/value chunk (non-causal, no dropout):
+ *     S = scale * Q K^T,  lse = logsumexp_k S,  out = softmax_k(S) V
+ * Replaces flash_attn_func(q, k, v, dropout_p=0, return_attn_probs=True) at
+ * core/attention.py:137-143 and :185-191, flash_attn_varlen_func at :314-324 and :366-376, and
+ * _flash_attn_varlen_forward at baseline/ulysses.py:99-113.
+ *
+ *  q, k, v        bf16.  Token t, head h, channel c of q is q[t*q_tok_stride + h*head_dim + c]
+ *                 (likewise k, v): [B,S,H,D] or packed [T,H,D] tensors, or slices of wider rows.
+ *                 Base pointers 16-byte aligned, strides multiples of 8 elements.
+ *  out            out_dtype DTB_F32 or DTB_BF16, same indexing with out_tok_stride.
+ *  lse            fp32, natural-log units, layout lse_layout over (nseg or 1, tokens, heads).
+ *  accumulate     0: write this chunk's state to (out, lse).
+ *                 1: merge this chunk's state INTO the state already held in (out, lse)
+ *                    (out must be DTB_F32) -- the update_out_and_lse step of utils.py:24-84 done
+ *                    in the kernel's epilogue.  A row whose lse holds -inf is treated as empty.
+ *  cu_seqlens_q/k NULL: dense batch -- nseg sequences of exactly seqlen_q query and seqlen_k key
+ *                 tokens each, stored back to back.  Otherwise device int32[nseg+1] cumulative
+ *                 offsets of a packed batch; seqlen_q / seqlen_k are then upper bounds on a
+ *                 segment's length.  Segment i of q attends segment i of k.  Rows of a segment
+ *                 with no keys get out = 0, lse = -inf.
+ *  total_q/k      number of tokens addressable behind q / k,v (rows of the 2-D view).
+ *  head_dim       64 or 128.
+ */
+DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
+                  int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
+                  void* out, int out_dtype, int64_t out_tok_stride,
+                  float* lse, int lse_layout, int accumulate,
+                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                  int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
+                  int num_heads, int head_dim, float softmax_scale, void* stream);
+
+/*
+ * N-way merge of partial softmax states in one pass over HBM:
+ *     lse_out = log sum_i exp(lse_i),   out = sum_i exp(lse_i - lse_out) * out_i
+ * Replaces the chains of update_out_and_lse (utils.py:24-84) at core/attention.py:110-116, :144,
+ * :193-196, :213 and proCache._merge_blocks (core/cache.py:28-46).
+ *
+ *  outs[i]       state i's values, [rows_bs, H, D] contiguous, dtype out_dtypes[i]
+ *  lses[i]       state i's fp32 lse over the same tokens, layout lse_layouts[i]
+ *  out / lse_out fp32 results (lse_out may be NULL); `out` and `lse_out` may alias input 0 only.
+ *  out_bf16      optional second copy of the result in bf16 (NULL to skip): the cast the
+ *                reference's callers apply right after the call
+ *                (executor/cogvideox/attention_processor.py:80).
+ *  batch, seq    tokens are [batch, seq]; they matter for DTB_LSE_BHS indexing only.
+ *  States whose lse is -inf on a row contribute nothing; a row empty in all states gets
+ *  out = 0, lse = -inf.
+ */
+DTB_API int dtb_merge_states(int nstates, const void* const* outs, const int* out_dtypes,
+                     const float* const* lses, const int* lse_layouts,
+                     float* out, float* lse_out, int lse_out_layout, void* out_bf16,
+                     int batch, int seq, int num_heads, int head_dim, void* stream);
+
+/*
+ * Strided copy of contiguous chunks: for every (i0,i1,i2) in [n0,n1,n2) copies chunk_bytes from
+ * src + i0*ss0 + i1*ss1 + i2*ss2 to dst + i0*ds0 + i1*ds1 + i2*ds2 (strides in bytes), for each of
+ * `npairs` (src, dst) pairs in one launch.  chunk_bytes, strides and pointers are multiples of 16.
+ * Used for the head<->sequence re-layouts around the Ulysses all-to-all, replacing the
+ * tensor_split + contiguous + cat copies of GroupCoordinator.all_to_all
+ * (core/group_coordinate.py:281-286).
+ */
+DTB_API int dtb_copy_chunks(int npairs, const void* const* srcs, void* const* dsts, int64_t chunk_bytes,
+                    int64_t n0, int64_t n1, int64_t n2,
+                    int64_t ss0, int64_t ss1, int64_t ss2,
+                    int64_t ds0, int64_t ds1, int64_t ds2, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DITANGO_B200_H_ */
