@@ -1,0 +1,218 @@
+"""Sequence-parallel attention with cached partial states: the per-layer object the model adapters
+call (`proAttention(layer_id, isp_group).attn(q, k, v)` / `.varlen_attn(...)`).
+
+Same contract as the reference's core/attention.py: inputs are this rank's contiguous bf16 chunk
+[B,S_loc,H,D] (or packed [T,H,D] with cu_seqlens), the result is a new fp32 tensor of that shape, the
+step index comes from the global set by the pipeline, the stride of (step, layer) from the global
+schedule, and every rank of the group must call in the same order.
+
+What is different underneath:
+  * partial attention runs in the sm_100a kernel; a block's fresh chunks are folded into ONE fp32
+    state by the kernel's accumulate epilogue instead of per-chunk merges (utils.py:24-84 of the
+    reference, called at core/attention.py:144, :193-196);
+  * cached blocks, the own chunk and the fresh block are combined by one N-way merge launch
+    (reference: a chain of pairwise merges at :110-116 and :213);
+  * KV chunks go owner -> consumer directly, K and V (and cu_seqlens) of a hop in one NCCL group,
+    received into two persistent slots that alternate; no clone before a send (reference: :51);
+  * the first-KV exchange is decided at block level; the reference decides it at chunk level
+    (:120), which makes it address itself and count its own chunk twice after some stride
+    transitions.  On schedules without such self-sends both give the same result.
+"""
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed
+
+from .. import ops as _engine
+from .._capi import LSE_BHS
+from ..logger import init_logger
+from ..timer import get_timer
+from ..utils import get_timestep
+from .cache import proCache
+from .config import get_config
+from .redundancy_map import get_redundancy_map
+from .schedule import StepPlan, plan_step
+
+logger = init_logger(__name__)
+
+# Two alternating receive slots per (device, shape, dtype), shared by all layers of the process:
+# layers run one after another, so one pair is enough.
+_SLOTS: Dict[Tuple, List[torch.Tensor]] = {}
+
+
+def _slot(tag: str, index: int, like: torch.Tensor) -> torch.Tensor:
+    key = (tag, like.device, tuple(like.shape), like.dtype)
+    if key not in _SLOTS:
+        _SLOTS[key] = [torch.empty_like(like, memory_format=torch.contiguous_format) for _ in range(2)]
+    return _SLOTS[key][index]
+
+
+def release_receive_slots():
+    _SLOTS.clear()
+
+
+class proAttention:
+    def __init__(self, layer_id: int, isp_group):
+        self.group = isp_group
+        self.isp_size = self.group.world_size
+        self.global_rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
+        self.local_chunk_id = self.group.rank_in_group
+        self.layer_id = layer_id
+        self.target_chunk_id = 0
+        # chunk pointer of every rank of the group for this layer; all ranks keep the same copy
+        self._pointers = [0] * self.isp_size
+        self.cache = proCache(isp_size=self.isp_size, layer_id=layer_id)
+        cfg = get_config()
+        self.use_ditango = bool(cfg.use_ditango) if cfg is not None else True
+        self.small_ring_stride = 8
+        self.measure_memory = False
+        self.measure_comm = False
+        self.last_lse: Optional[torch.Tensor] = None       # [B,H,S] / [H,T] of the last result
+        self.stats = dict(calls=0, chunks_attended=0, chunks_received=0, bytes_received=0,
+                          cached_blocks_merged=0, merge_launches=0)
+        self._comm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
+
+    # ------------------------------------------------------------------ transport
+    def _commit_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
+        """Post this rank's sends of its own chunk and its receive for `hop` as one batch."""
+        me = self.local_chunk_id
+        src = plan.recv_from(me, hop)
+        recv = None
+        for dst in plan.send_to(me, hop):
+            for t in payload:
+                self.group.p2p_isend(t, dst=dst)
+        if src is not None:
+            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(f"kv{i}", hop & 1, t)) for i, t in enumerate(payload))
+            self.stats["chunks_received"] += 1
+            self.stats["bytes_received"] += sum(t.numel() * t.element_size() for t in payload)
+        self.group.p2p_commit()
+        return recv
+
+    def _wait_hop(self):
+        if self.measure_comm and torch.cuda.is_available():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            self.group.p2p_wait()
+            b.record()
+            self._comm_events.append((a, b))
+        else:
+            self.group.p2p_wait()
+
+    def exposed_comm_ms(self, reset: bool = True) -> float:
+        """Time the compute stream spent blocked on incoming KV since the last reset."""
+        if not self._comm_events:
+            return 0.0
+        torch.cuda.synchronize()
+        total = sum(a.elapsed_time(b) for a, b in self._comm_events)
+        if reset:
+            self._comm_events = []
+        return total
+
+    # ------------------------------------------------------------------ the call
+    def _run(self, query, key, value, cu_q=None, cu_kv=None, max_q=None, max_kv=None):
+        N, me = self.isp_size, self.local_chunk_id
+        rmap = get_redundancy_map()
+        t = get_timestep()
+        stride = rmap.get_curr_isp_stride(t, self.layer_id)
+        next_stride = rmap.get_next_isp_stride(t, self.layer_id)
+        if t == 0:
+            self.cache.set_block_size_mb(value)
+        if not self.cache.pass_memory_check(next_stride, self.layer_id):
+            next_stride = N
+        assert N % stride == 0, f"Does not support this ISP stride {stride} for SP size {N}"
+        if stride > self.small_ring_stride and self.use_ditango:
+            # the reference switches to a two-level ring here (groups larger than one node)
+            assert stride % self.small_ring_stride == 0, \
+                f"Does not support this ISP stride {stride} for overlap ring strategy"
+
+        plan = plan_step(N, stride, self._pointers)
+        mine = plan.ranks[me]
+        nblk = N // stride
+        packed = cu_q is not None
+        payload = (key, value, cu_kv) if packed else (key, value)
+        keep_chunks = stride == N and next_stride != N        # fine-grained store after a full refresh
+        keep_block = stride != N and next_stride != N
+
+        def attend(kv, into=None):
+            kk, vv = kv[0], kv[1]
+            kw = {}
+            if packed:
+                kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
+            self.stats["chunks_attended"] += 1
+            if into is None:
+                return _engine.flash_partial(query, kk, vv, lse_layout=LSE_BHS, **kw)
+            return _engine.flash_partial(query, kk, vv, out=into[0], lse=into[1], accumulate=True,
+                                         lse_layout=LSE_BHS, **kw)
+
+        # 1. cached blocks (every block but the target one)
+        states = []
+        if stride != N:
+            for i in range(nblk - 1):
+                o, l = self.cache.get_block((mine.target_block + 1 + i) % nblk)
+                if l is not None:
+                    states.append((o, l, LSE_BHS))
+            self.stats["cached_blocks_merged"] += len(states)
+
+        # 2. own chunk first when the target block is a foreign one; its flash overlaps hop 0
+        own = None
+        incoming = None
+        if mine.own_first:
+            incoming = self._commit_hop(plan, 0, payload)
+            own = attend(payload)
+            self._wait_hop()
+
+        # 3. the target block's chunks
+        fresh = None
+        chunk_states = []
+        for hop in range(stride):
+            current = payload if mine.owners[hop] == me else incoming
+            if hop + 1 < stride:
+                incoming = self._commit_hop(plan, hop + 1, payload)
+            if mine.owners[hop] == me:
+                own = attend(payload)
+            elif keep_chunks:
+                st = attend(current)
+                self.cache.store_block(mine.owners[hop], st[0], st[1])
+                chunk_states.append((st[0], st[1], LSE_BHS))
+            elif keep_block:
+                fresh = attend(current, into=fresh)
+            else:
+                own = attend(current, into=own)          # nothing is kept: fold into the result
+            if hop + 1 < stride:
+                self._wait_hop()
+
+        # 4. store the fresh block, combine everything in one pass
+        if fresh is not None:
+            self.cache.store_block(mine.target_block, fresh[0], fresh[1])
+            chunk_states.append((self.cache.out_block_cache[mine.target_block], fresh[1], LSE_BHS))
+        others = states + chunk_states
+        if others:
+            out, lse = _engine.merge_states([(own[0], own[1], LSE_BHS)] + others, out=own[0], lse_out=own[1],
+                                            lse_out_layout=LSE_BHS)
+            self.stats["merge_launches"] += 1
+        else:
+            out, lse = own
+
+        # 5. pointers and cache layout for the next step
+        self._pointers = plan.pointers_after
+        self.target_chunk_id = self._pointers[me]
+        self.cache.update_cache_blocks(next_stride, self.target_chunk_id // next_stride)
+        self.last_lse = lse
+        self.stats["calls"] += 1
+        rmap.record_out_redundancy(timestep=t, layer_id=self.layer_id, curr_out=out)
+        return out
+
+    @get_timer("oAttn")
+    def attn(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+        """query, key, value: [B, S_loc, H, D] -> fp32 [B, S_loc, H, D]."""
+        return self._run(query, key, value)
+
+    @get_timer("varlen oAttn")
+    def varlen_attn(self, query, key, value, cu_seqlens_q=None, cu_seqlens_kv=None,
+                    max_seqlen_q=None, max_seqlen_kv=None, batch_size=1) -> torch.Tensor:
+        """Packed variant: query, key, value [T, H, D]; the KV owner's cu_seqlens travels with its K,V."""
+        if cu_seqlens_q is None and cu_seqlens_kv is None and max_seqlen_q is None and max_seqlen_kv is None:
+            logger.warning("cu_seqlens_q not provided, using normal attention instead.")
+            return self.attn(query, key, value)
+        return self._run(query, key, value, cu_q=cu_seqlens_q, cu_kv=cu_seqlens_kv,
+                         max_q=max_seqlen_q, max_kv=max_seqlen_kv)

@@ -1,0 +1,92 @@
+"""Worker bodies for the multi-process CPU tests (spawned with torch.multiprocessing)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _setup(rank, world, port):
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank),
+                      LOCAL_RANK=str(rank))
+    torch.set_num_threads(1)
+    from tests import cpu_engine
+    cpu_engine.install()
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.config import init_config
+    cfg = init_config(None, make_output_dir=False)
+    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=rank, backend="gloo")
+    c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+    ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+    return cfg, ps
+
+
+def ring_worker(rank, world, port, case, ret):
+    cfg, ps = _setup(rank, world, port)
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.utils import update_timestep
+    from oracle.ring_oracle import drifting_qkv
+    div = case["dividers"]
+    cfg.num_layers, cfg.num_inference_steps = 1, len(div)
+    rm = init_redundancy_map(cfg)
+    for t, d in enumerate(div):
+        rm.divider_map[t, 0] = d
+    layer = proAttention(0, ps.get_isp_group())
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    data = drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"])
+    outs = []
+    for t in range(len(div)):
+        update_timestep(t)
+        q, k, v = data[t]
+        lo, hi = rank * S // world, (rank + 1) * S // world
+        ql, kl, vl = (x[:, lo:hi].contiguous() for x in (q, k, v))
+        if case.get("cu") is not None:
+            cu = torch.tensor(case["cu"][rank], dtype=torch.int32)
+            o = layer.varlen_attn(ql[0], kl[0], vl[0], cu_seqlens_q=cu, cu_seqlens_kv=cu,
+                                  max_seqlen_q=hi - lo, max_seqlen_kv=hi - lo)[None]
+        else:
+            o = layer.attn(ql, kl, vl)
+        outs.append(o.clone())
+    ret[rank] = (torch.stack(outs), dict(layer.stats))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def ulysses_worker(rank, world, port, case, ret):
+    cfg, ps = _setup(rank, world, port)
+    from ditango_b200.baseline.ulysses import ulysses_attention
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    g = torch.Generator().manual_seed(case["seed"])
+    q, k, v = (torch.randn(B, S, H, D, generator=g) for _ in range(3))
+    lo, hi = rank * S // world, (rank + 1) * S // world
+    out = ulysses_attention(q[:, lo:hi].contiguous(), k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous(),
+                            group=ps.get_isp_group())
+    ret[rank] = out.float()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def collectives_worker(rank, world, port, ret):
+    cfg, ps = _setup(rank, world, port)
+    g = ps.get_isp_group()
+    x = torch.arange(2 * 3 * 4, dtype=torch.float32).view(2, 3, 4) + 100 * rank
+    res = dict(
+        a2a=g.all_to_all(x, scatter_dim=2, gather_dim=1),
+        gather=g.all_gather(x, dim=1),
+        reduce=g.all_reduce(x.clone()),
+        ranks=(g.world_size, g.rank_in_group, g.ranks),
+    )
+    buf = torch.empty(3)
+    g.p2p_isend(torch.full((3,), float(rank)), dst=(rank + 1) % world)
+    got = g.p2p_irecv(src=(rank - 1) % world, out=buf)
+    g.p2p_commit()
+    g.p2p_wait()
+    res["p2p"] = got.clone()
+    ret[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
