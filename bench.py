@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the sequence-parallel attention path on N B200s of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload hunyuan|cogvideox|stepvideo]
+                    [--mode ditango|ring|ulysses] [--impl ours|reference]
+
+One step = one denoising step = one call of every layer's attention object (proAttention.attn, or
+ulysses_attention) on that step's Q/K/V.  Synthetic inputs of the named model's attention shape:
+step-0 Q,K,V ~ N(0,1), every later step adds N(0, 0.05^2) (HunyuanVideo: Q and K RMS-normalised);
+the same tensors feed every layer, each layer keeping its own cache and pointer.  The sequence is
+sharded over the N ranks (strong scaling); the redundancy schedule is Bernoulli(p) per (step, layer)
+drawn from seed 0, legalised and screened, with the first three steps at full stride.
+
+Rank 0 prints ONE JSON line.  `value` counts the FLOPs the kernels executed (4*B*H*Sq*Sk*D per
+chunk pair), summed over ranks, divided by the max-over-ranks device time; `e2e` is the same metric
+with every layer's inputs copied from pinned host memory and its output copied back inside the
+timed region.  `--impl reference` times the CPU restatement of the reference's path (oracle/) on
+the host cores on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, H, D, S, layers, steps, reuse probability, rms-normalised q/k
+    "hunyuan": dict(B=1, H=24, D=128, S=119056, layers=60, steps=50, p=0.7, rms=True,
+                    desc="HunyuanVideo 720p attention shape (33x45x80 video + 256 text tokens)"),
+    "cogvideox": dict(B=2, H=48, D=64, S=17776, layers=42, steps=50, p=0.6, rms=False,
+                      desc="CogVideoX-5B self-attention shape (13x30x45 video + 226 text tokens)"),
+    "stepvideo": dict(B=2, H=48, D=128, S=54808, layers=48, steps=50, p=0.5, rms=False,
+                      desc="Stepvideo-T2V self-attention shape (26x34x62 tokens)"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(tensor=float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1401.5))),
+                    tensor_burst=float(d.get("bf16_tflops", 1669.0)), hbm=float(d.get("hbm_gbs", 6544.3)),
+                    source="measured")
+    return dict(tensor=1400.0, tensor_burst=1590.0, hbm=6650.0, source="fallback")
+
+
+def draw_dividers(steps, layers, world, p, seed=0):
+    """Bernoulli(p) reuse per (step, layer); a reuse cell takes a divider drawn uniformly from
+    {2,4,8} that divides the group size; step 0 is a full refresh."""
+    rng = np.random.RandomState(seed)
+    choices = [d for d in (2, 4, 8) if d <= world and world % d == 0]
+    div = np.ones((steps, layers), dtype=np.int64)
+    if choices:
+        for t in range(1, steps):
+            for l in range(layers):
+                if rng.rand() < p:
+                    div[t, l] = choices[rng.randint(len(choices))]
+    return div
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------ ours
+def make_inputs(w, rank, world, device, seed=0):
+    B, H, D, S = w["B"], w["H"], w["D"], w["S"]
+    S_loc = S // world
+    g = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+    raw = [torch.randn(B, S_loc, H, D, generator=g, device=device, dtype=torch.float32) for _ in range(3)]
+    return raw, g
+
+
+def step_inputs(raw, gen, w, first):
+    """Apply the per-step drift in place and return this step's bf16 q, k, v."""
+    if not first:
+        for x in raw:
+            x.add_(torch.randn(x.shape, generator=gen, device=x.device, dtype=x.dtype), alpha=0.05)
+    q, k, v = raw
+    if w["rms"]:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + 1e-6)
+    return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from ditango_b200 import _capi, ops
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core.group_coordinate import SingleRankGroup
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.baseline.ulysses import ulysses_attention
+    from ditango_b200.utils import update_timestep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _capi.check(_capi.load().dtb_device_supported(), "dtb_device_supported")
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+    if w["S"] % world or (args.mode == "ulysses" and w["H"] % world):
+        raise SystemExit(f"workload {args.workload} does not shard over {world} ranks")
+
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = w["layers"], w["steps"]
+    cfg.use_ditango = args.mode == "ditango"
+    if world > 1:
+        ps.init_distributed_environment(world_size=world, rank=rank, local_rank=local_rank, backend="nccl")
+        c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+        ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+        group = ps.get_isp_group()
+    else:
+        group = SingleRankGroup(device)
+    rm = init_redundancy_map(cfg, world_size=world)
+    reuse_cells = 0
+    if args.mode == "ditango" and world > 1:
+        rm.divider_map = torch.from_numpy(draw_dividers(w["steps"], w["layers"], world, w["p"]))
+        rm._refine_divider_map()
+        rm.screen_self_sends()
+    layers = [proAttention(l, group) for l in range(w["layers"])]
+    raw, gen = make_inputs(w, rank, world, device)
+    B, H, D, S = w["B"], w["H"], w["D"], w["S"]
+    S_loc = S // world
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(t, qkv, out_sink=None):
+        update_timestep(t % w["steps"])
+        q, k, v = qkv
+        last = None
+        for l in range(w["layers"]):
+            if args.mode == "ulysses":
+                last = ulysses_attention(q, k, v, group=group)
+            else:
+                last = layers[l].attn(q, k, v)
+        return last
+
+    # ---------------------------------------------------------------- device-resident timing
+    total_steps = args.warmup + args.steps
+    for t in range(args.warmup):
+        one_step(t, step_inputs(raw, gen, w, first=(t == 0)))
+    # Inputs of the timed steps are produced before the clock starts and stay resident in HBM; when
+    # K steps of inputs would not fit a 24 GB budget the prepared steps are cycled.
+    step_bytes = 3 * B * S_loc * H * D * 2
+    n_prepared = max(1, min(args.steps, int(24e9 // step_bytes)))
+    prepared = [step_inputs(raw, gen, w, first=False) for _ in range(n_prepared)]
+    barrier()
+    status = ops.read_status()
+    if status != 0:
+        raise SystemExit(f"kernel status {status} during warm-up")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ops.LaunchLog.reset(with_events=True)
+    for L in layers:
+        L.measure_comm = world > 1
+        L.exposed_comm_ms()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for t in range(args.warmup, total_steps):
+        one_step(t, prepared[(t - args.warmup) % n_prepared])
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = ops.LaunchLog.count
+    flash_ms = [a.elapsed_time(b) for a, b, _ in ops.LaunchLog.events]
+    flash_flops = [f for _, _, f in ops.LaunchLog.events]
+    exposed_ms = sum(L.exposed_comm_ms() for L in layers)
+    ops.LaunchLog.reset(with_events=False)
+    for L in layers:
+        L.measure_comm = False
+    status = ops.read_status()
+    if status != 0:
+        raise SystemExit(f"kernel status {status} in the timed region")
+
+    # ---------------------------------------------------------------- end-to-end (host buffers)
+    e2e_steps = args.steps
+    q, k, v = prepared[0]
+    host_in = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for x in (q, k, v)]
+    for h, x in zip(host_in, (q, k, v)):
+        h.copy_(x)
+    out_dtype = torch.bfloat16 if args.mode == "ulysses" else torch.float32
+    host_out = torch.empty(q.shape, dtype=out_dtype).pin_memory()
+    dev_in = [torch.empty_like(x) for x in (q, k, v)]
+    h2d = sum(h.numel() * h.element_size() for h in host_in) * w["layers"]
+    d2h = host_out.numel() * host_out.element_size() * w["layers"]
+
+    def e2e_step(t):
+        update_timestep(t % w["steps"])
+        for l in range(w["layers"]):
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+            o = ulysses_attention(*dev_in, group=group) if args.mode == "ulysses" else layers[l].attn(*dev_in)
+            host_out.copy_(o, non_blocking=True)
+    t_next = total_steps
+    e2e_step(t_next)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.LaunchLog.reset(with_events=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(t_next + 1 + i)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    e2e_flops = sum(f for _, _, f in ops.LaunchLog.events)
+    ops.LaunchLog.reset(with_events=False)
+
+    # ---------------------------------------------------------------- reduce over ranks
+    stats = torch.tensor([elapsed_ms, e2e_ms, exposed_ms], device=device, dtype=torch.float64)
+    sums = torch.tensor([sum(flash_flops), e2e_flops, sum(flash_ms), float(len(flash_ms)), float(launches)],
+                        device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    elapsed_ms, e2e_ms, exposed_ms = stats.tolist()
+    tot_flops, tot_e2e_flops, tot_flash_ms, n_flash, tot_launches = sums.tolist()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(w, 1, sample_seq=args.cpu_seq, min_seconds=10.0)
+    if rank == 0:
+        peaks = measured_peaks()
+        value = tot_flops / (elapsed_ms * 1e-3) / 1e12
+        per_launch_tflops = (tot_flops / n_flash) / (tot_flash_ms / n_flash * 1e-3) / 1e12 if n_flash else 0.0
+        full_flops = 4.0 * B * H * float(S) * S * D * w["layers"] * args.steps
+        line = {
+            "metric": "attention TFLOP/s (executed FLOPs, whole job) and ms per denoising step",
+            "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(elapsed_ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}; B={B} H={H} D={D} S={S}, {w['layers']} layers/step, "
+                                   f"mode={args.mode}, sequence sharded over {world} rank(s)",
+                       "mode": args.mode, "global_batch": B, "seq_len": S, "layers_per_step": w["layers"],
+                       "l2": "inputs larger than L2 (Q,K,V of one layer call exceed 126 MB)",
+                       "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0},
+            "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
+            "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
+            "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
+            "roofline": {"bound": "tensor", "achieved": round(per_launch_tflops, 2), "peak": peaks["tensor"],
+                         "unit": "TFLOP/s", "frac": round(per_launch_tflops / peaks["tensor"], 4),
+                         "peak_kind": f"{peaks['source']} sustained bf16 cuBLAS GEMM; burst {peaks['tensor_burst']}",
+                         "kernel": f"flash_fwd_kernel<{D}>", "launches_timed": int(n_flash),
+                         "traffic": None},
+            "clocks": clocks,
+            "e2e": {"value": round(tot_e2e_flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                    "ms_per_step": round(e2e_ms / e2e_steps, 3),
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(tot_launches),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------- CPU legs
+def cpu_baseline(w, world, sample_seq=None, steps=1, min_seconds=0.0):
+    """Times the CPU restatement of the reference's path (oracle/) on the host cores: one layer call
+    per step on a sequence of `sample_seq` tokens per rank (same B, H, D), ranks simulated as
+    threads of one process."""
+    from oracle import ring_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores // world))
+    B, H, D = w["B"], w["H"], w["D"]
+    s_loc = sample_seq or 4096
+    S = s_loc * world
+    data = O.drifting_qkv(B, S, H, D, 1, seed=0, dtype=torch.bfloat16, rms_norm_qk=w["rms"])
+    t0 = time.perf_counter()
+    flops, calls = 0.0, 0
+    while calls < steps or (min_seconds and time.perf_counter() - t0 < min_seconds):
+        q, k, v = data[0]
+        if world == 1:
+            for h0 in range(0, H, 4):         # head groups keep the score matrix under ~2 GB
+                O.partial_attention(q[:, :, h0:h0 + 4], k[:, :, h0:h0 + 4], v[:, :, h0:h0 + 4])
+        else:
+            O.run_ring_group(world, [1], data, partial_dtype=torch.bfloat16)
+        flops += 4.0 * B * H * float(S) * S * D
+        calls += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(flops / dt / 1e12, 4), "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "seconds": round(dt, 2),
+            "sample": f"{calls} layer call(s) of the oracle at B={B} H={H} D={D} S={S} ({world} simulated rank(s)); "
+                      f"full workload is S={w['S']} x {w['layers']} layers per step"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = dict(WORKLOADS[args.workload])
+    t_all = []
+    cpu = None
+    for i in range(args.warmup + args.steps):
+        cpu = cpu_baseline(w, args.gpus, sample_seq=args.cpu_seq, steps=1, min_seconds=4.0)
+        if i >= args.warmup:
+            t_all.append(cpu)
+    value = statistics.mean(c["value"] for c in t_all)
+    secs = statistics.mean(c["seconds"] for c in t_all)
+    cpu = dict(t_all[-1], value=round(value, 4))
+    B, H, D, S = w["B"], w["H"], w["D"], w["S"]
+    full_step_flops = 4.0 * B * H * float(S) * S * D * w["layers"]
+    line = {
+        "impl": "reference", "metric": "attention TFLOP/s (executed FLOPs, whole job) and ms per denoising step",
+        "value": round(value, 4), "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(full_step_flops / (value * 1e12) * 1e3, 1), "ms_per_step_kind": "extrapolated from the sample",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 inputs, fp32 arithmetic",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}; B={B} H={H} D={D} S={S}, {w['layers']} layers/step",
+                   "mode": "ring", "global_batch": B, "seq_len": S, "layers_per_step": w["layers"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="hunyuan", choices=sorted(WORKLOADS))
+    ap.add_argument("--mode", default="ditango", choices=["ditango", "ring", "ulysses"])
+    ap.add_argument("--layers", type=int, default=0, help="override layers per step (debugging only)")
+    ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        print("warning: fewer than 3 warm-up steps", file=sys.stderr)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

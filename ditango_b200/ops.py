@@ -13,6 +13,19 @@ from . import _capi
 from ._capi import DTB_BF16, DTB_F32, LSE_BHS, LSE_BSH
 
 
+class LaunchLog:
+    """Optional accounting of kernel launches made through this module.  `count` always runs; with
+    `events` enabled every flash launch is bracketed by two CUDA events on the launching stream so
+    a benchmark can read per-launch device time and the FLOPs each launch executed."""
+    count = 0
+    events = None            # list of (start_event, end_event, flops) while enabled
+
+    @classmethod
+    def reset(cls, with_events: bool = False):
+        cls.count = 0
+        cls.events = [] if with_events else None
+
+
 def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -91,12 +104,21 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise _capi.ExtensionError("out must be float32 or bfloat16")
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    ev = None
+    if LaunchLog.events is not None:
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
     rc = lib.dtb_flash_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), _tok_stride(q), _tok_stride(k), _tok_stride(v),
         out.data_ptr(), odt, _tok_stride(out), lse.data_ptr(), lse_layout, int(accumulate),
         cu_seqlens_q.data_ptr() if packed else None, cu_seqlens_k.data_ptr() if packed else None,
         nseg, sq, sk, Tq, Tk, H, D, scale, _stream_ptr())
     _capi.check(rc, "dtb_flash_fwd")
+    LaunchLog.count += 1
+    if ev is not None:
+        ev[1].record()
+        # dense: every query row meets every key row of its sequence; packed: upper bound by maxima
+        LaunchLog.events.append((ev[0], ev[1], 4.0 * nseg * H * sq * sk * D))
     return out, lse
 
 
@@ -136,6 +158,7 @@ def merge_states(states: Sequence[Tuple[torch.Tensor, torch.Tensor, int]], *,
         n, outs, dts, lses, lays, out.data_ptr(), lse_out.data_ptr() if lse_out is not None else None,
         lse_out_layout, out_bf16.data_ptr() if out_bf16 is not None else None, B, S, H, D, _stream_ptr())
     _capi.check(rc, "dtb_merge_states")
+    LaunchLog.count += 1
     return out, lse_out
 
 
@@ -152,3 +175,4 @@ def copy_chunks(pairs: Sequence[Tuple[torch.Tensor, torch.Tensor]], chunk_bytes:
         srcs[i], dsts[i] = s.data_ptr(), d.data_ptr()
     rc = lib.dtb_copy_chunks(n, srcs, dsts, chunk_bytes, *extents, *src_strides, *dst_strides, _stream_ptr())
     _capi.check(rc, "dtb_copy_chunks")
+    LaunchLog.count += 1

@@ -90,3 +90,52 @@ def collectives_worker(rank, world, port, ret):
     ret[rank] = res
     dist.barrier()
     dist.destroy_process_group()
+
+
+def gpu_ring_worker(rank, world, port, case, ret):
+    """NCCL ranks, one GPU each, real kernels: proAttention on bf16 inputs."""
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from ditango_b200 import ops
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.baseline.ulysses import ulysses_attention
+    from ditango_b200.utils import update_timestep
+    from oracle.ring_oracle import drifting_qkv
+    cfg = init_config(None, make_output_dir=False)
+    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=rank, backend="nccl")
+    c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+    ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+    div = case["dividers"]
+    cfg.num_layers, cfg.num_inference_steps = 1, len(div)
+    rm = init_redundancy_map(cfg)
+    for t, d in enumerate(div):
+        rm.divider_map[t, 0] = d
+    layer = proAttention(0, ps.get_isp_group())
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    data = drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"], dtype=torch.bfloat16)
+    lo, hi = rank * S // world, (rank + 1) * S // world
+    outs = []
+    for t in range(len(div)):
+        update_timestep(t)
+        ql, kl, vl = (x[:, lo:hi].contiguous().cuda() for x in data[t])
+        if case.get("cu") is not None:
+            cu = torch.tensor(case["cu"][rank], dtype=torch.int32).cuda()
+            o = layer.varlen_attn(ql[0], kl[0], vl[0], cu_seqlens_q=cu, cu_seqlens_kv=cu,
+                                  max_seqlen_q=hi - lo, max_seqlen_kv=hi - lo)[None]
+        else:
+            o = layer.attn(ql, kl, vl)
+        outs.append(o.float().cpu())
+    uly = None
+    if case.get("ulysses"):
+        ql, kl, vl = (x[:, lo:hi].contiguous().cuda() for x in data[0])
+        uly = ulysses_attention(ql, kl, vl, group=ps.get_isp_group()).float().cpu()
+    status = ops.read_status()
+    ret[rank] = (torch.stack(outs), dict(layer.stats), uly, status)
+    dist.barrier()
+    dist.destroy_process_group()
