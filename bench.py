@@ -377,6 +377,55 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_micro(args):
+    """Single-kernel timing on one GPU (also the small case the ncu captures under profiles/ use):
+    one chunk pair of the workload at S/shard tokens (`flash`), an n-state merge at that shape
+    (`merge`), or the Ulysses re-layout copy (`copy`).  Prints one JSON line."""
+    from ditango_b200 import ops
+    torch.cuda.set_device(0)
+    w = WORKLOADS[args.workload]
+    B, H, D, S = w["B"], w["H"], w["D"], w["S"] // args.shard
+    peaks = measured_peaks()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, dt=torch.float32: torch.randn(*shape, generator=g, device=dev, dtype=torch.float32).to(dt)
+    if args.micro == "flash":
+        q, k, v = (rnd(B, S, H, D, dt=torch.bfloat16) for _ in range(3))
+        out = torch.empty(B, S, H, D, device=dev, dtype=torch.float32)
+        lse = torch.empty(B, H, S, device=dev, dtype=torch.float32)
+        fn = lambda: ops.flash_partial(q, k, v, out=out, lse=lse)
+        work, unit, peak, bound = 4.0 * B * H * S * S * D, "TFLOP/s", peaks["tensor_burst"], "tensor"
+    elif args.micro == "merge":
+        n = args.states
+        st = [(rnd(B, S, H, D), rnd(B, H, S), ops.LSE_BHS) for _ in range(n)]
+        fn = lambda: ops.merge_states(st, out=st[0][0], lse_out=st[0][1], lse_out_layout=ops.LSE_BHS)
+        work, unit, peak, bound = float((n + 1) * B * S * H * (D * 4 + 4)), "GB/s", peaks["hbm"], "hbm"
+    else:
+        N = 8
+        x = [rnd(B, S, H, D, dt=torch.bfloat16) for _ in range(3)]
+        y = [torch.empty(N, B, S, H // N, D, device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        C = (H // N) * D * 2
+        fn = lambda: ops.copy_chunks(list(zip(x, y)), C, (N, B, S), (C, S * H * D * 2, H * D * 2), (B * S * C, S * C, C))
+        work, unit, peak, bound = float(2 * 3 * B * S * H * D * 2), "GB/s", peaks["hbm"], "hbm"
+    for _ in range(max(1, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(max(1, args.steps)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    rate = work / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
+    print(json.dumps({"micro": args.micro, "workload": args.workload, "shape": dict(B=B, S=S, H=H, D=D),
+                      "states": args.states if args.micro == "merge" else None, "ms": round(ms, 4),
+                      "achieved": round(rate, 1), "unit": unit, "peak": peak, "frac": round(rate / peak, 4),
+                      "status": ops.read_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -388,7 +437,12 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override layers per step (debugging only)")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy"], help="time one kernel and exit")
+    ap.add_argument("--shard", type=int, default=8, help="--micro: tokens = S / shard")
+    ap.add_argument("--states", type=int, default=4, help="--micro merge: number of states")
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     if args.warmup < 3 and args.impl == "ours":
         print("warning: fewer than 3 warm-up steps", file=sys.stderr)
     if args.impl == "reference":
