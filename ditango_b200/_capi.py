@@ -7,7 +7,9 @@ import ctypes
 import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libditango_b200.so")
+# DITANGO_B200_LIB points at a library built elsewhere (same ABI); default: the in-tree build.
+_LIB_PATH = os.environ.get("DITANGO_B200_LIB") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "lib", "libditango_b200.so")
 _lib = None
 
 DTB_F32, DTB_BF16 = 0, 1

@@ -94,6 +94,10 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 }  // namespace
 
+#ifdef DTB_FLASH_TIMING
+namespace dtb { cudaError_t read_flash_timing(long long* host, int n); }
+#endif
+
 extern "C" {
 
 DTB_API int dtb_version(void) { return 100; }
@@ -253,5 +257,11 @@ DTB_API int dtb_copy_chunks(int npairs, const void* const* srcs, void* const* ds
   if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "dtb_copy_chunks launch failed: %s", cudaGetErrorString(e));
   return DTB_OK;
 }
+
+#ifdef DTB_FLASH_TIMING
+DTB_API int dtb_debug_flash_timing(long long* host, int n) {
+  return dtb::read_flash_timing(host, n) == cudaSuccess ? 0 : DTB_ERR_CUDA;
+}
+#endif
 
 }  // extern "C"

@@ -1,17 +1,23 @@
 // Partial-attention forward for sm_100a: one launch computes, for every query row of a chunk, the
 // softmax-attention state (out, lse) against ONE key/value chunk.
 //
-// CTA = 256 query rows of one (segment, head): two 128-row Q tiles that ping-pong on the tensor
-// core.  Warp roles (320 threads):
+// CTA = 256 query rows of one (segment, head): two 128-row Q tiles share the tensor core.  Warp roles
+// (320 threads):
 //   warps 0-3   softmax group 0: one thread per row of Q tile 0
 //   warps 4-7   softmax group 1: one thread per row of Q tile 1
 //   warp  8     TMA producer: Q tiles once, then K_j, V_j tiles through a shared-memory ring
 //   warp  9     MMA issuer (one elected thread): S_i = Q_i K_j^T and O_i += P_i V_j via tcgen05.mma
 // Tensor memory (512 columns x 128 lanes of fp32): S_0 [0,128), S_1 [128,256), O_0 [256,256+D),
-// O_1 [256+D,256+2D).  P_i (bf16) overwrites the first 64 columns of S_i and is consumed by the PV
-// MMA straight from tensor memory.  Issue order on the tensor pipe:
-//   S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
-// so the softmax of one Q tile runs while the pipe works on the other tile.
+// O_1 [256+D,256+2D).
+//   D = 128: the map is full, so P_i (bf16) overwrites the first 64 columns of S_i.  Issue order
+//       S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
+//     the softmax of one Q tile runs while the pipe works on the other tile.
+//   D = 64: 128 columns are left, so P_i gets its own columns [384 + 64 i, 448 + 64 i).  S_i(j+1) is
+//     then issued as soon as the softmax group has pulled S_i(j) into registers, ahead of PV_i(j):
+//       S0(0) S1(0) | S0(j+1) S1(j+1) PV0(j) PV1(j) | ...
+//     and in steady state a softmax group never waits for the tensor pipe.
+// P is handed to the MMA issuer in two halves (keys 0-63, 64-127) so the first PV steps start while
+// the second half is still being exponentiated.
 // Running max is kept lazily: O is rescaled only when the max grew by more than 2^8, which bounds
 // every probability by 2^8 and keeps bf16 P exact enough; the final normalisation undoes it.
 #include "flash_fwd_sm100.cuh"
@@ -30,7 +36,6 @@ constexpr int kThreads = 320;
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kSlabBytes = 128 * 128;   // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
-constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -39,12 +44,37 @@ struct Cfg {
   static constexpr int kSlabs = D / 64;
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kStages = (D == 128) ? 4 : 6;
-  static constexpr int kBars = 1 + 2 * kStages + 2 + 2 + 1;
+  // P in its own tensor-memory columns and S_i(j+1) issued ahead of PV_i(j)
+  static constexpr bool kDecoupled = (256 + 2 * D + 128 <= 512);
+  // sibling warps of the two softmax groups alternate in the exp phase
+  static constexpr bool kTurns = kDecoupled;
+  // of every 4 score pairs, this many take the polynomial exp2 instead of the ex2 unit
+#ifdef DTB_EMU_PAIRS
+  static constexpr int kEmuPairs = DTB_EMU_PAIRS;
+#else
+  static constexpr int kEmuPairs = 0;
+#endif
+  // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[4], s_free[2], pv_done[2], exp_turn[8], o_final
+  static constexpr int kBars = 1 + 2 * kStages + 2 + 4 + 2 + 2 + 8 + 1;
   static constexpr int kSmemBytes = 1024 + (kQT + kStages) * kTileBytes + kBars * 8 + 16;
   static constexpr uint32_t kTmemCols = 512;
-  static constexpr uint32_t kColS = 0;      // + tile * 128
-  static constexpr uint32_t kColO = 256;    // + tile * D
+  static constexpr uint32_t kColS = 0;                                  // + tile * 128
+  static constexpr uint32_t kColO = 256;                                // + tile * D
+  static constexpr uint32_t kColP = kDecoupled ? 256 + 2 * D : 0;       // + tile * kStrideP
+  static constexpr uint32_t kStrideP = kDecoupled ? 64 : 128;
 };
+
+#ifdef DTB_FLASH_TIMING
+// Development aid: per-phase SM clock stamps of one CTA (roles: softmax group 0, 1, MMA issuer).
+__device__ long long g_flash_timing[3 * 48 * 8];
+#define DTB_STAMP(role, j, phase)                                                                      \
+  do {                                                                                                 \
+    if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 48)                             \
+      g_flash_timing[((role) * 48 + (j)) * 8 + (phase)] = clock64();                                   \
+  } while (0)
+#else
+#define DTB_STAMP(role, j, phase) do { } while (0)
+#endif
 
 __device__ __forceinline__ void report(int* status, int code) {
   atomicCAS(status, 0, code);
@@ -65,6 +95,23 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, in
     }
   }
   return true;
+}
+
+// 2^x for a pair of fp32 values without the ex2 unit: x is clamped to >= -126, split as n + f with
+// n = round(x) (magic-number add) and f in [-0.5, 0.5], 2^f by a cubic (max relative error 7.5e-5,
+// far below the bf16 rounding of P), and n added into the exponent field.
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& p0, float& p1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const float t0 = x0 + 12582912.f, t1 = x1 + 12582912.f;
+  const float f0 = x0 - (t0 - 12582912.f), f1 = x1 - (t1 - 12582912.f);
+  float q0 = fmaf(0.0551716685f, f0, 0.2426111251f), q1 = fmaf(0.0551716685f, f1, 0.2426111251f);
+  q0 = fmaf(q0, f0, 0.6932609677f);
+  q1 = fmaf(q1, f1, 0.6932609677f);
+  q0 = fmaf(q0, f0, 0.9999280572f);
+  q1 = fmaf(q1, f1, 0.9999280572f);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 
 __device__ __forceinline__ int64_t lse_index(const FlashParams& p, int seg, int head, int q_pos, int64_t tok) {
@@ -88,9 +135,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + C::kStages;
-  uint64_t* s_full = kv_empty + C::kStages;
-  uint64_t* p_full = s_full + 2;
-  uint64_t* o_final = p_full + 2;
+  uint64_t* s_full = kv_empty + C::kStages;   // [tile]: S_tile(j) is in tensor memory
+  uint64_t* p_full = s_full + 2;              // [tile*2 + half]: P of keys [64 half, 64 half + 64) written
+  uint64_t* s_free = p_full + 4;              // [tile]: S_tile(j) has been read into registers (decoupled)
+  uint64_t* pv_done = s_free + 2;             // [tile]: PV_tile(j) has completed (decoupled)
+  uint64_t* exp_turn = pv_done + 2;           // [tile*4 + quarter]: the sibling warp finished its exp phase
+  uint64_t* o_final = exp_turn + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kBars);
 
   const int warp = threadIdx.x >> 5;
@@ -133,6 +183,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     return;
   }
 
+  // Position of K_j / V_j in the order the ring carries them.
+  //   coupled:   K_0 V_0 K_1 V_1 ...                 (K_j at 2j, V_j at 2j+1)
+  //   decoupled: K_0 K_1 V_0 K_2 V_1 ... V_{n-1}     (K_{j+1} is consumed before V_j)
+  auto k_slot = [&](int j) { return C::kDecoupled ? (j == 0 ? 0 : 2 * j - 1) : 2 * j; };
+  auto v_slot = [&](int j) { return C::kDecoupled ? (j < n_tiles - 1 ? 2 * j + 2 : 2 * j + 1) : 2 * j + 1; };
+
   // ------------------------------------------------------------------ set-up
   if (threadIdx.x == kTmaWarp * 32) {
     mbar_init(q_full, 1);
@@ -142,8 +198,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], kBM);
+      mbar_init(&s_free[i], kBM);
+      mbar_init(&pv_done[i], 1);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&exp_turn[i], 32);
+    for (int i = 0; i < 4; ++i) mbar_init(&p_full[i], kBM);
     mbar_init(o_final, 1);
     fence_mbar_init();
   }
@@ -170,14 +229,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int s = 0; s < C::kSlabs; ++s)
           tma_load_2d(s_q + t * C::kTileBytes + s * kSlabBytes, &tm_q, q_full, head * D + s * 64,
                       q_begin + q0 + t * kBM);
-      const int n_loads = 2 * n_tiles;     // K_0 V_0 K_1 V_1 ...
+      const int n_loads = 2 * n_tiles;
       for (int it = 0; it < n_loads; ++it) {
+        bool is_v;
+        int j;
+        if (C::kDecoupled) {
+          if (it == 0) { is_v = false; j = 0; }
+          else if (it == n_loads - 1) { is_v = true; j = n_tiles - 1; }
+          else if (it & 1) { is_v = false; j = (it + 1) >> 1; }
+          else { is_v = true; j = (it - 2) >> 1; }
+        } else {
+          is_v = it & 1;
+          j = it >> 1;
+        }
         const int stage = it % C::kStages;
         const int round = it / C::kStages;
         if (round > 0 && !wait_or_abort(&kv_empty[stage], (round - 1) & 1, p.status, 11)) break;
         mbar_expect_tx(&kv_full[stage], C::kTileBytes);
-        const CUtensorMap* tm = (it & 1) ? &tm_v : &tm_k;
-        const int row = k_begin + (it >> 1) * kBN;
+        const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+        const int row = k_begin + j * kBN;
         for (int s = 0; s < C::kSlabs; ++s)
           tma_load_2d(s_kv + stage * C::kTileBytes + s * kSlabBytes, tm, &kv_full[stage], head * D + s * 64, row);
       }
@@ -200,52 +270,94 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mma_ss(tmem_base + C::kColS + tile * kBN, a, b, idesc_qk, k16 > 0);
         }
       };
-      auto issue_pv = [&](int tile, int stage, bool acc) {
+      // half h covers keys [64 h, 64 h + 64) of the tile: four K=16 steps
+      auto issue_pv = [&](int tile, int stage, int half, bool acc) {
 #pragma unroll
-        for (int k16 = 0; k16 < kBN / 16; ++k16) {
+        for (int kk = 0; kk < kBN / 32; ++kk) {
+          const int k16 = half * (kBN / 32) + kk;
           const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kTileBytes + k16 * 2048, kSlabBytes, 1024);
-          mma_ts(tmem_base + C::kColO + tile * D, tmem_base + C::kColS + tile * kBN + k16 * 8, b, idesc_pv,
+          mma_ts(tmem_base + C::kColO + tile * D, tmem_base + C::kColP + tile * C::kStrideP + k16 * 8, b, idesc_pv,
                  (acc || k16 > 0) ? 1u : 0u);
         }
       };
       auto stage_of = [&](int it) { return it % C::kStages; };
       auto parity_of = [&](int it) { return static_cast<uint32_t>((it / C::kStages) & 1); };
+      auto wait_kv = [&](int it, int code) {
+        return wait_or_abort(&kv_full[stage_of(it)], parity_of(it), p.status, code);
+      };
+      // both halves of P_tile(j), then PV_tile(j)
+      auto pv_when_ready = [&](int tile, int j, int stage) {
+        if (!wait_or_abort(&p_full[tile * 2], j & 1, p.status, 24 + tile)) return false;
+        DTB_STAMP(2, j, 3 + 2 * tile);
+        tc_fence_after();
+        issue_pv(tile, stage, 0, j > 0);
+        if (!wait_or_abort(&p_full[tile * 2 + 1], j & 1, p.status, 26 + tile)) return false;
+        tc_fence_after();
+        issue_pv(tile, stage, 1, true);
+        return true;
+      };
 
       bool ok = wait_or_abort(q_full, 0, p.status, 21);
-      if (ok) ok = wait_or_abort(&kv_full[stage_of(0)], parity_of(0), p.status, 22);
+      if (ok) ok = wait_kv(k_slot(0), 22);
       if (ok) {
         tc_fence_after();
-        issue_s(0, stage_of(0));
+        issue_s(0, stage_of(k_slot(0)));
         mma_commit(&s_full[0]);
-        issue_s(1, stage_of(0));
+        issue_s(1, stage_of(k_slot(0)));
         mma_commit(&s_full[1]);
-        mma_commit(&kv_empty[stage_of(0)]);
+        mma_commit(&kv_empty[stage_of(k_slot(0))]);
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int it_v = 2 * j + 1, it_kn = 2 * j + 2;
         const bool more = (j + 1 < n_tiles);
-        ok = wait_or_abort(&kv_full[stage_of(it_v)], parity_of(it_v), p.status, 23);
-        if (!ok) break;
-        ok = wait_or_abort(&p_full[0], j & 1, p.status, 24);
-        if (!ok) break;
-        tc_fence_after();
-        issue_pv(0, stage_of(it_v), j > 0);
-        if (more) {
-          ok = wait_or_abort(&kv_full[stage_of(it_kn)], parity_of(it_kn), p.status, 25);
+        const int it_v = v_slot(j), it_kn = k_slot(j + 1);
+        DTB_STAMP(2, j, 0);
+        if (C::kDecoupled) {
+          if (more) {
+            ok = wait_kv(it_kn, 25);
+            for (int tile = 0; ok && tile < 2; ++tile) {
+              ok = wait_or_abort(&s_free[tile], j & 1, p.status, 28 + tile);
+              if (!ok) break;
+              tc_fence_after();
+              issue_s(tile, stage_of(it_kn));
+              mma_commit(&s_full[tile]);
+            }
+            if (!ok) break;
+            mma_commit(&kv_empty[stage_of(it_kn)]);
+          }
+          DTB_STAMP(2, j, 1);
+          ok = wait_kv(it_v, 23);
           if (!ok) break;
-          tc_fence_after();
-          issue_s(0, stage_of(it_kn));
-          mma_commit(&s_full[0]);
-        }
-        ok = wait_or_abort(&p_full[1], j & 1, p.status, 26);
-        if (!ok) break;
-        tc_fence_after();
-        issue_pv(1, stage_of(it_v), j > 0);
-        mma_commit(&kv_empty[stage_of(it_v)]);
-        if (more) {
-          issue_s(1, stage_of(it_kn));
-          mma_commit(&s_full[1]);
-          mma_commit(&kv_empty[stage_of(it_kn)]);
+          DTB_STAMP(2, j, 2);
+          for (int tile = 0; ok && tile < 2; ++tile) {
+            ok = pv_when_ready(tile, j, stage_of(it_v));
+            if (ok) mma_commit(&pv_done[tile]);
+            DTB_STAMP(2, j, 4 + 2 * tile);
+          }
+          if (!ok) break;
+          mma_commit(&kv_empty[stage_of(it_v)]);
+        } else {
+          ok = wait_kv(it_v, 23);
+          if (!ok) break;
+          DTB_STAMP(2, j, 1);
+          ok = pv_when_ready(0, j, stage_of(it_v));
+          if (!ok) break;
+          if (more) {
+            ok = wait_kv(it_kn, 25);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(0, stage_of(it_kn));
+            mma_commit(&s_full[0]);
+          }
+          DTB_STAMP(2, j, 2);
+          ok = pv_when_ready(1, j, stage_of(it_v));
+          if (!ok) break;
+          mma_commit(&kv_empty[stage_of(it_v)]);
+          if (more) {
+            issue_s(1, stage_of(it_kn));
+            mma_commit(&s_full[1]);
+            mma_commit(&kv_empty[stage_of(it_kn)]);
+          }
+          DTB_STAMP(2, j, 3);
         }
       }
       if (ok) mma_commit(o_final);
@@ -257,41 +369,75 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t s_taddr = lane_base + C::kColS + tile * kBN;
+    const uint32_t p_taddr = lane_base + C::kColP + tile * C::kStrideP;
     const uint32_t o_taddr = lane_base + C::kColO + tile * D;
     const float c = p.scale_log2;
     float m = -INFINITY;   // running max of raw scores (lazily updated)
     float l = 0.f;         // running sum of exp2((s - m) * c)
     bool ok = true;
+    const bool stamp = (lane == 0 && (warp & 3) == 0);
+    (void)stamp;
 
     for (int j = 0; j < n_tiles; ++j) {
+      if (stamp) DTB_STAMP(tile, j, 0);
       ok = wait_or_abort(&s_full[tile], j & 1, p.status, 31 + tile);
       if (!ok) break;
+      if (stamp) DTB_STAMP(tile, j, 1);
       tc_fence_after();
       uint32_t sr[kBN];
-#pragma unroll
-      for (int q = 0; q < kBN / 32; ++q) tmem_ld32(s_taddr + q * 32, sr + q * 32);
+      const bool tail = (j == n_tiles - 1) && (k_len & (kBN - 1)) != 0;
+      const int valid = tail ? k_len - j * kBN : kBN;
+      tmem_ld32(s_taddr, sr);
+      tmem_ld32(s_taddr + 32, sr + 32);
       tmem_wait_ld();
-      if (j == n_tiles - 1 && (k_len & (kBN - 1)) != 0) {
-        const int valid = k_len - j * kBN;
+      // the second half of the row lands while the first half is reduced
+      tmem_ld32(s_taddr + 64, sr + 64);
+      tmem_ld32(s_taddr + 96, sr + 96);
+      if (tail) {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i)
+        for (int i = 0; i < kBN / 2; ++i)
           if (i >= valid) sr[i] = 0xff800000u;   // -inf
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < kBN; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+      for (int i = 0; i < kBN / 2; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
       }
-      const float m_new = fmaxf(fmaxf(m, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
+      tmem_wait_ld();
+      if (C::kDecoupled) {
+        // S_tile(j) now lives in registers: the tensor pipe may overwrite it with S_tile(j+1)
+        tc_fence_before();
+        mbar_arrive(&s_free[tile]);
+      }
+      if (tail) {
+#pragma unroll
+        for (int i = kBN / 2; i < kBN; ++i)
+          if (i >= valid) sr[i] = 0xff800000u;
+      }
+#pragma unroll
+      for (int i = kBN / 2; i < kBN; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+      }
+      if (stamp) DTB_STAMP(tile, j, 2);
+      const float m_new = fmaxf(max3(m, mx0, mx1), fmaxf(mx2, mx3));
+      if (C::kDecoupled && j > 0) {
+        // PV_tile(j-1) must have drained before its P columns are rewritten or O is rescaled.  (In the
+        // coupled order the commit behind s_full(j) already covers it.)
+        ok = wait_or_abort(&pv_done[tile], (j - 1) & 1, p.status, 33 + tile);
+        if (!ok) break;
+        tc_fence_after();
+      }
       if (j == 0) {
         m = m_new;
       } else {
         const bool grow = (m_new - m) * c > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
-          // PV(j-1) of this tile has completed: the commit behind s_full covers it.
           const float f = ex2((m - m_new) * c);
 #pragma unroll
           for (int q = 0; q < D / 32; ++q) {
@@ -307,23 +453,54 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           m = m_new;
         }
       }
-      const float mc = m * c;
-      float sum0 = 0.f, sum1 = 0.f;
+      if (stamp) DTB_STAMP(tile, j, 3);
+      // p = 2^(s*c - m*c): the ex2 unit (16 results per clock per SM) against 4*D tensor FLOPs per
+      // score; kEmuPairs of every four pairs go through the FMA/ALU pipes instead.
+      if (C::kTurns) {
+        // Warp w of group 0 and warp w of group 1 sit on the same scheduler and feed the same ex2
+        // unit.  They take turns in the exp phase (0, 1, 0, 1, ...): side by side each phase would
+        // take twice as long and the unit would idle while both warps load and reduce their next
+        // rows.  Group 0's first turn is free (parity trick).
+        ok = wait_or_abort(&exp_turn[tile * 4 + (warp & 3)], tile == 0 ? ((j & 1) ^ 1) : (j & 1), p.status, 35 + tile);
+        if (!ok) break;
+      }
+      const float nmc = -m * c;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
       uint32_t pk[kBN / 2];
 #pragma unroll
-      for (int i = 0; i < kBN; i += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[i]), c, -mc));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[i + 1]), c, -mc));
-        sum0 += p0;
-        sum1 += p1;
-        pk[i >> 1] = pack_bf16x2(p0, p1);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int g = half * 8; g < half * 8 + 8; ++g) {
+#pragma unroll
+          for (int pr = 0; pr < 4; ++pr) {
+            const int i = g * 8 + pr * 2;
+            const float x0 = fmaf(__uint_as_float(sr[i]), c, nmc);
+            const float x1 = fmaf(__uint_as_float(sr[i + 1]), c, nmc);
+            float p0, p1;
+            if (pr >= 4 - C::kEmuPairs) {
+              exp2_poly_pair(x0, x1, p0, p1);
+            } else {
+              p0 = ex2(x0);
+              p1 = ex2(x1);
+            }
+            if (pr & 1) {
+              sum2 += p0;
+              sum3 += p1;
+            } else {
+              sum0 += p0;
+              sum1 += p1;
+            }
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          }
+        }
+        tmem_st32(p_taddr + half * 32, pk + half * 32);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[tile * 2 + half]);
+        if (stamp) DTB_STAMP(tile, j, 4 + half);
       }
-      l += sum0 + sum1;
-      tmem_st32(s_taddr, pk);
-      tmem_st32(s_taddr + 32, pk + 32);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_full[tile]);
+      if (C::kTurns) mbar_arrive(&exp_turn[(tile ^ 1) * 4 + (warp & 3)]);
+      l += (sum0 + sum1) + (sum2 + sum3);
     }
 
     if (ok) ok = wait_or_abort(o_final, 0, p.status, 41);
@@ -421,6 +598,12 @@ cudaError_t launch_flash(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   flash_fwd_kernel<D><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   return cudaGetLastError();
 }
+
+#ifdef DTB_FLASH_TIMING
+cudaError_t read_flash_timing(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_flash_timing, sizeof(long long) * n);
+}
+#endif
 
 template cudaError_t launch_flash<64>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FlashParams&, cudaStream_t);
 template cudaError_t launch_flash<128>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const FlashParams&, cudaStream_t);
