@@ -242,17 +242,43 @@ def run_ours(args):
         h.copy_(x)
     out_dtype = torch.bfloat16 if args.mode == "ulysses" else torch.float32
     host_out = torch.empty(q.shape, dtype=out_dtype).pin_memory()
-    dev_in = [torch.empty_like(x) for x in (q, k, v)]
+    # Two device input slots: the copies of layer l+1 run on a copy stream while layer l computes;
+    # results leave on a second copy stream.  Every byte still crosses PCIe inside the timed region.
+    dev_in = [[torch.empty_like(x) for x in (q, k, v)] for _ in range(2)]
     h2d = sum(h.numel() * h.element_size() for h in host_in) * w["layers"]
     d2h = host_out.numel() * host_out.element_size() * w["layers"]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(t):
         update_timestep(t % w["steps"])
+        main = torch.cuda.current_stream()
+
+        def fetch(l):
+            slot = l & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_free[slot])
+                for d, h in zip(dev_in[slot], host_in):
+                    d.copy_(h, non_blocking=True)
+                ev_in[slot].record(s_in)
+        for slot in range(2):
+            ev_free[slot].record(main)
+        fetch(0)
         for l in range(w["layers"]):
-            for d, h in zip(dev_in, host_in):
-                d.copy_(h, non_blocking=True)
-            o = ulysses_attention(*dev_in, group=group) if args.mode == "ulysses" else layers[l].attn(*dev_in)
-            host_out.copy_(o, non_blocking=True)
+            slot = l & 1
+            if l + 1 < w["layers"]:
+                fetch(l + 1)
+            main.wait_event(ev_in[slot])
+            o = ulysses_attention(*dev_in[slot], group=group) if args.mode == "ulysses" else layers[l].attn(*dev_in[slot])
+            ev_free[slot].record(main)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                host_out.copy_(o, non_blocking=True)
+                o.record_stream(s_out)
+        main.wait_stream(s_out)
     t_next = total_steps
     e2e_step(t_next)
     barrier()

@@ -3,7 +3,7 @@
 // A "row" is one (token, head) pair: D values per state plus one log-sum-exp per state.  A group of
 // D/4 lanes owns a row (4 fp32 or 4 bf16 values per lane, 128-bit / 64-bit accesses); lane i of the
 // group fetches lse_i, the group reduces max and sum with shuffles, and every lane then pulls the
-// weight of state i from lane i.  Each thread keeps kUnroll rows in flight to cover HBM latency.
+// weight of state i from lane i.
 // Traffic per row: reads sum_i (D * sizeof(state i) + 4) bytes, writes 4*D + 4 (+ 2*D) bytes.
 #include "merge_states.cuh"
 
@@ -41,109 +41,139 @@ __device__ __forceinline__ void st_bf4(uint16_t* p, float4 v) {
   asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
 
-__device__ __forceinline__ int64_t lse_offset(int layout, int64_t row, int H, int S) {
-  // row = (b*S + s)*H + h
-  if (layout == 1) return row;
-  const int64_t tok = row / H;
-  const int h = static_cast<int>(row - tok * H);
-  const int64_t b = tok / S;
-  const int64_t s = tok - b * S;
-  return (b * H + h) * S + s;
+// Offset of row = (b*S + s)*H + h in an lse tensor.  Rows fit 32 bits (checked by the launcher), so
+// the two divisions are 32-bit.
+__device__ __forceinline__ uint32_t lse_offset(int layout, uint32_t row, uint32_t H, uint32_t S) {
+  if (layout == 1) return row;                    // [B,S,H]
+  const uint32_t tok = row / H;
+  const uint32_t h = row - tok * H;
+  const uint32_t b = tok / S;
+  const uint32_t s = tok - b * S;
+  return (b * H + h) * S + s;                     // [B,H,S]
 }
 
 }  // namespace
 
-// G = lanes per row = D/4.
-template <int G, int kUnroll>
-__global__ void __launch_bounds__(256) merge_states_kernel(const MergeParams p) {
+// G = lanes per row = D/4.  U rows per group in flight, states fetched CH at a time: every thread
+// keeps CH*U 16-byte loads outstanding and issues them before it touches the weights, so the lse
+// round trip and the value round trips overlap instead of queueing behind one another.
+template <int G, int U, int CH>
+__global__ void __launch_bounds__(128) merge_states_kernel(const MergeParams p) {
   constexpr int D = G * 4;
-  const int lane_in_group = threadIdx.x % G;
   constexpr int kGroupsPerWarp = 32 / G;
+  const int lane_in_group = threadIdx.x % G;
   const int64_t warp_id = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / 32;
   const int64_t n_warps = static_cast<int64_t>(gridDim.x) * blockDim.x / 32;
   const int group_in_warp = (threadIdx.x % 32) / G;
   const unsigned full = 0xffffffffu;
   const int n = p.nstates;
 
+  auto load_chunk = [&](int c0, int64_t base, float4 (&v)[CH][U]) {
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      if (c0 + k < n) {
+        const bool f32 = p.out_dtype[c0 + k] == 0;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t row = base + u;
+          if (row < p.rows) {
+            const int64_t off = row * D + lane_in_group * 4;
+            v[k][u] = f32 ? ld_f4(static_cast<const float*>(p.outs[c0 + k]) + off)
+                          : ld_bf4(static_cast<const uint16_t*>(p.outs[c0 + k]) + off);
+          } else {
+            v[k][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
+    }
+  };
+
   // The loop bound is the same for every lane of a warp (shuffles below use the full mask); rows
   // past the end are guarded individually.
-  for (int64_t wbase = warp_id * kGroupsPerWarp * kUnroll; wbase < p.rows;
-       wbase += n_warps * kGroupsPerWarp * kUnroll) {
-    const int64_t base = wbase + group_in_warp * kUnroll;
-    float w[kUnroll];        // this lane's weight (state index = lane_in_group)
-    float lse_out[kUnroll];
+  for (int64_t wbase = warp_id * kGroupsPerWarp * U; wbase < p.rows; wbase += n_warps * kGroupsPerWarp * U) {
+    const int64_t base = wbase + group_in_warp * U;
+    float my[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int64_t row = base + u;
-      float my = -INFINITY;
+      my[u] = -INFINITY;
       if (row < p.rows && lane_in_group < n)
-        my = p.lse[lane_in_group][lse_offset(p.lse_layout[lane_in_group], row, p.H, p.S)];
-      float mx = my;
+        my[u] = p.lse[lane_in_group][lse_offset(p.lse_layout[lane_in_group], static_cast<uint32_t>(row), p.H, p.S)];
+    }
+    float4 v[CH][U];
+    load_chunk(0, base, v);
+
+    float w[U];        // this lane's weight (state index = lane_in_group)
+    float lse_out[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float mx = my[u];
 #pragma unroll
       for (int o = G / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o, G));
-      const float e = (my == -INFINITY) ? 0.f : __expf(my - mx);
+      const float e = (my[u] == -INFINITY) ? 0.f : __expf(my[u] - mx);
       float sum = e;
 #pragma unroll
       for (int o = G / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(full, sum, o, G);
       w[u] = (sum > 0.f) ? e / sum : 0.f;
       lse_out[u] = (sum > 0.f) ? mx + __logf(sum) : -INFINITY;
     }
-    float4 acc[kUnroll];
+    float4 acc[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int i = 0; i < n; ++i) {
-      float4 v[kUnroll];
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < n; c0 += CH) {
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t row = base + u;
-        if (row < p.rows) {
-          const int64_t off = row * D + lane_in_group * 4;
-          v[u] = (p.out_dtype[i] == 0) ? ld_f4(static_cast<const float*>(p.outs[i]) + off)
-                                       : ld_bf4(static_cast<const uint16_t*>(p.outs[i]) + off);
-        } else {
-          v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < CH; ++k) {
+        if (c0 + k < n) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const float wi = __shfl_sync(full, w[u], c0 + k, G);
+            // a state with weight 0 may hold anything (even inf/nan): it must not reach the sum
+            if (wi != 0.f) {
+              acc[u].x = fmaf(wi, v[k][u].x, acc[u].x);
+              acc[u].y = fmaf(wi, v[k][u].y, acc[u].y);
+              acc[u].z = fmaf(wi, v[k][u].z, acc[u].z);
+              acc[u].w = fmaf(wi, v[k][u].w, acc[u].w);
+            }
+          }
         }
       }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const float wi = __shfl_sync(full, w[u], i, G);
-        // a state with weight 0 may hold anything (even inf/nan): it must not reach the sum
-        if (wi != 0.f) {
-          acc[u].x = fmaf(wi, v[u].x, acc[u].x);
-          acc[u].y = fmaf(wi, v[u].y, acc[u].y);
-          acc[u].z = fmaf(wi, v[u].z, acc[u].z);
-          acc[u].w = fmaf(wi, v[u].w, acc[u].w);
-        }
-      }
+      if (c0 + CH < n) load_chunk(c0 + CH, base, v);
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int64_t row = base + u;
       if (row < p.rows) {
         const int64_t off = row * D + lane_in_group * 4;
         st_f4(p.out + off, acc[u]);
         if (p.out_bf16 != nullptr) st_bf4(p.out_bf16 + off, acc[u]);
         if (p.lse_out != nullptr && lane_in_group == 0)
-          p.lse_out[lse_offset(p.lse_out_layout, row, p.H, p.S)] = lse_out[u];
+          p.lse_out[lse_offset(p.lse_out_layout, static_cast<uint32_t>(row), p.H, p.S)] = lse_out[u];
       }
     }
   }
 }
 
-cudaError_t launch_merge(const MergeParams& p, int head_dim, int sm_count, cudaStream_t stream) {
-  const int threads = 256;
-  const int G = head_dim / 4;
-  constexpr int kUnroll = 4;
-  const int64_t groups_needed = (p.rows + kUnroll - 1) / kUnroll;
-  int64_t blocks_needed = (groups_needed * G + threads - 1) / threads + 1;
-  int64_t cap = static_cast<int64_t>(sm_count) * 8;      // 8 resident CTAs of 256 threads per SM
+template <int U, int CH>
+static cudaError_t launch_merge_cfg(const MergeParams& p, int G, int sm_count, cudaStream_t stream) {
+  constexpr int kThreads = 128;
+  const int64_t groups_needed = (p.rows + U - 1) / U;
+  const int64_t blocks_needed = (groups_needed * G + kThreads - 1) / kThreads + 1;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 7;      // resident CTAs of 128 threads per SM at ~70 registers
   int blocks = static_cast<int>(blocks_needed < cap ? blocks_needed : cap);
   if (blocks < 1) blocks = 1;
   if (G == 16)
-    merge_states_kernel<16, kUnroll><<<blocks, threads, 0, stream>>>(p);
+    merge_states_kernel<16, U, CH><<<blocks, kThreads, 0, stream>>>(p);
   else
-    merge_states_kernel<32, kUnroll><<<blocks, threads, 0, stream>>>(p);
+    merge_states_kernel<32, U, CH><<<blocks, kThreads, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+// Rows per thread x states per fetch are chosen so that about eight 16-byte loads are outstanding
+// per thread whatever the number of states.
+cudaError_t launch_merge(const MergeParams& p, int head_dim, int sm_count, cudaStream_t stream) {
+  const int G = head_dim / 4;
+  if (p.rows >= (1ll << 31)) return cudaErrorInvalidValue;
+  return launch_merge_cfg<2, 4>(p, G, sm_count, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
