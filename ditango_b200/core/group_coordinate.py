@@ -19,8 +19,14 @@ class GroupCoordinator:
         self.cpu_group = None
         self.p2p_ops = []
         self.p2p_reqs = None
+        pg_options = None
+        if torch_distributed_backend == "nccl":
+            # NCCL's transfer kernels run on a high-priority stream: when an SM frees up they are placed
+            # ahead of the attention kernel's remaining CTAs, so a KV hop overlaps the attention on
+            # the chunk that is already here instead of queueing behind it.
+            pg_options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
         for ranks in group_ranks:
-            device_group = dist.new_group(ranks, backend=torch_distributed_backend)
+            device_group = dist.new_group(ranks, backend=torch_distributed_backend, pg_options=pg_options)
             cpu_group = dist.new_group(ranks, backend="gloo")
             if self.rank in ranks:
                 self.ranks = list(ranks)
