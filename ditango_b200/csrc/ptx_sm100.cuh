@@ -132,7 +132,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t
 // Instruction descriptor, kind::f16, bf16 x bf16 -> fp32, dense.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N, bool a_mn_major, bool b_mn_major) {
   return (1u << 4)                               // D format fp32
-         | (1u << 7)                             // A format bf16
+         | (1u << 7)                             // A format bf16 (A and B must be the same 16-bit type)
          | (1u << 10)                            // B format bf16
          | (static_cast<uint32_t>(a_mn_major) << 15)
          | (static_cast<uint32_t>(b_mn_major) << 16)
@@ -178,28 +178,6 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-// Two fp32 values in one 64-bit register, for the packed f32x2 arithmetic of sm_100.
-__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void upk2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ void upk2u(uint64_t v, uint32_t& lo, uint32_t& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
