@@ -19,6 +19,7 @@ MERGE_MAX_STATES = 16
 EXPORTS = (
     "dtb_version", "dtb_last_error", "dtb_device_supported", "dtb_read_status",
     "dtb_flash_fwd", "dtb_merge_states", "dtb_copy_chunks",
+    "dtb_drift_scratch_bytes", "dtb_drift_accumulate",
 )
 
 
@@ -59,6 +60,10 @@ def load():
     lib.dtb_copy_chunks.argtypes = [
         c_int, POINTER(c_void_p), POINTER(c_void_p), c_int64, c_int64, c_int64, c_int64,
         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]
+    lib.dtb_drift_scratch_bytes.restype = c_int64
+    lib.dtb_drift_scratch_bytes.argtypes = [c_int64]
+    lib.dtb_drift_accumulate.restype = c_int
+    lib.dtb_drift_accumulate.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]
     _lib = lib
     return lib
 

@@ -188,17 +188,33 @@ class RedundancyMap:
     def enable_auto_setting(self):
         self.auto_setting = True
         self.redundancy_map = torch.zeros(self.num_timesteps, self.num_layers, dtype=torch.float)
+        self._device_map = None
         self.prev_out = [None] * self.num_layers
 
     def record_out_redundancy(self, timestep: int, layer_id: int, curr_out: torch.Tensor):
-        """Profiling only (core/redundancy_map.py:174-197): accumulate mean|cur-prev| / mean|prev|."""
+        """Profiling only (core/redundancy_map.py:174-197): add the relative L1 drift of this layer's
+        output against the previous step's to cell (timestep, layer).  On the device the sums, the
+        ratio and the accumulation happen in one kernel with no host round trip; the map is brought
+        back by finish_auto_setting()."""
         if not self.auto_setting:
             return
         prev = self.prev_out[layer_id]
         if prev is not None:
-            dist = ((curr_out - prev).abs().mean() / prev.abs().mean()).item()
-            self.redundancy_map[timestep, layer_id] += dist
+            if curr_out.is_cuda:
+                from .. import ops
+                if self._device_map is None:
+                    self._device_map = torch.zeros(self.num_timesteps, self.num_layers, dtype=torch.float32,
+                                                   device=curr_out.device)
+                ops.drift_accumulate(curr_out.float(), prev.float(), self._device_map[timestep, layer_id])
+            else:
+                d = (curr_out.double() - prev.double()).abs().mean() / (prev.double().abs().mean() + 1e-8)
+                self.redundancy_map[timestep, layer_id] += float(d)
         self.prev_out[layer_id] = curr_out
+
+    def _collect_device_map(self):
+        if getattr(self, "_device_map", None) is not None:
+            self.redundancy_map = self.redundancy_map + self._device_map.cpu()
+            self._device_map = None
 
     def finished_one_round(self):
         self.calc_round += 1
@@ -207,6 +223,7 @@ class RedundancyMap:
     def finish_auto_setting(self):
         if not self.auto_setting:
             return
+        self._collect_device_map()
         if torch.distributed.is_initialized() and self.redundancy_map is not None:
             dev = get_usp_group().device
             red = self.redundancy_map.to(dev)

@@ -3,6 +3,7 @@
 #include "../../include/ditango_b200.h"
 
 #include "flash_fwd_sm100.cuh"
+#include "drift_stats.cuh"
 #include "merge_states.cuh"
 
 #include <cuda.h>
@@ -255,6 +256,25 @@ DTB_API int dtb_copy_chunks(int npairs, const void* const* srcs, void* const* ds
   if (n0 * n1 * n2 == 0) return DTB_OK;
   cudaError_t e = dtb::launch_copy_chunks(p, npairs, d->sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "dtb_copy_chunks launch failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
+DTB_API int64_t dtb_drift_scratch_bytes(int64_t n) { return dtb::drift_scratch_bytes(n < 0 ? 0 : n); }
+
+DTB_API int dtb_drift_accumulate(const float* cur, const float* prev, int64_t n, float* accum,
+                                 void* scratch, int64_t scratch_bytes, void* stream) {
+  if (n < 0) return fail(DTB_ERR_ARG, "dtb_drift_accumulate: negative length");
+  if (!accum || !scratch || (n > 0 && (!cur || !prev))) return fail(DTB_ERR_ARG, "dtb_drift_accumulate: null pointer");
+  if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DTB_ERR_ARG, "dtb_drift_accumulate: scratch must be 256-byte aligned");
+  if (scratch_bytes < dtb::drift_scratch_bytes(n))
+    return fail(DTB_ERR_ARG, "dtb_drift_accumulate: scratch of %lld bytes is smaller than the %lld needed for n = %lld",
+                static_cast<long long>(scratch_bytes), static_cast<long long>(dtb::drift_scratch_bytes(n)), static_cast<long long>(n));
+  if (dtb::drift_blocks(n) >= (1ll << 31)) return fail(DTB_ERR_ARG, "dtb_drift_accumulate: n too large");
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != DTB_OK) return rc;
+  cudaError_t e = dtb::launch_drift_stats(cur, prev, n, accum, static_cast<unsigned char*>(scratch), static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "dtb_drift_accumulate launch failed: %s", cudaGetErrorString(e));
   return DTB_OK;
 }
 

@@ -176,3 +176,32 @@ def copy_chunks(pairs: Sequence[Tuple[torch.Tensor, torch.Tensor]], chunk_bytes:
     rc = lib.dtb_copy_chunks(n, srcs, dsts, chunk_bytes, *extents, *src_strides, *dst_strides, _stream_ptr())
     _capi.check(rc, "dtb_copy_chunks")
     LaunchLog.count += 1
+
+
+_DRIFT_SCRATCH = {}
+
+
+def drift_accumulate(cur: torch.Tensor, prev: torch.Tensor, accum: torch.Tensor,
+                     scratch: Optional[torch.Tensor] = None):
+    """accum (one fp32 element on the device) += relative L1 drift of `cur` against `prev`
+    (fp32, same number of elements), without a host round trip.  `scratch` defaults to a per-device
+    buffer kept by this module and grown on demand."""
+    lib = _capi.load()
+    _need_cuda(cur, prev, accum, scratch)
+    if cur.dtype != torch.float32 or prev.dtype != torch.float32 or accum.dtype != torch.float32:
+        raise _capi.ExtensionError("drift_accumulate takes fp32 tensors")
+    if cur.numel() != prev.numel() or accum.numel() != 1:
+        raise _capi.ExtensionError("cur and prev must have equal sizes; accum must hold one element")
+    cur, prev = cur.contiguous(), prev.contiguous()
+    n = cur.numel()
+    need = lib.dtb_drift_scratch_bytes(n)
+    if scratch is None:
+        key = cur.device
+        scratch = _DRIFT_SCRATCH.get(key)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=cur.device)
+            _DRIFT_SCRATCH[key] = scratch
+    rc = lib.dtb_drift_accumulate(cur.data_ptr(), prev.data_ptr(), n, accum.data_ptr(), scratch.data_ptr(),
+                                  scratch.numel(), _stream_ptr())
+    _capi.check(rc, "dtb_drift_accumulate")
+    LaunchLog.count += 1

@@ -124,6 +124,23 @@ DTB_API int dtb_copy_chunks(int npairs, const void* const* srcs, void* const* ds
                     int64_t ss0, int64_t ss1, int64_t ss2,
                     int64_t ds0, int64_t ds1, int64_t ds2, void* stream);
 
+/*
+ * Drift metric of the redundancy-profiling pass, accumulated on the device:
+ *     *accum += mean|cur - prev| / (mean|prev| + 1e-8)      over positions where neither is NaN
+ * (mean|cur| instead when mean|prev| < 1e-6; +inf when no position is valid).  Replaces rel_l1
+ * (utils.py:202-267) as called from RedundancyMap.record_out_redundancy
+ * (core/redundancy_map.py:174-197), which reads three means back to the host per layer and step.
+ *
+ *  cur, prev     fp32 [n] on the device
+ *  accum         one fp32 on the device (for example an element of the [steps, layers] map)
+ *  scratch       device memory of at least dtb_drift_scratch_bytes(n) bytes, 256-byte aligned, whose
+ *                first 4 bytes are zero before the first call; the call leaves them zero, so one
+ *                buffer serves any number of calls that do not overlap on the device.
+ */
+DTB_API int64_t dtb_drift_scratch_bytes(int64_t n);
+DTB_API int dtb_drift_accumulate(const float* cur, const float* prev, int64_t n, float* accum,
+                                 void* scratch, int64_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

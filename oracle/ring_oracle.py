@@ -23,6 +23,7 @@ Reference locations restated here (paths relative to the reference project root)
   * the ring / reuse state machine: core/attention.py:73-237 (dense) and :239-419 (varlen).
   * Ulysses head/sequence all-to-all attention: baseline/ulysses.py:51-124 with
     core/group_coordinate.py:281-286.
+  * the drift metric of the redundancy-profiling pass: utils.py:202-267 (`rel_l1`).
 
 All ranks of a group are simulated inside one process: each rank runs the state machine in
 its own thread and point-to-point messages travel through in-memory mailboxes, so the order
@@ -498,6 +499,25 @@ def ulysses_attention(q_shards, k_shards, v_shards) -> List[torch.Tensor]:
         outs.append(o.reshape(B, -1, Hn * D))
     back = all_to_all_views(outs, 1, 2)
     return [x.view(B, S_loc, H, D) for x in back]
+
+
+# --------------------------------------------------------------------------------------
+# Redundancy profiling metric (utils.py:202-267 of the reference)
+# --------------------------------------------------------------------------------------
+
+def rel_l1(new: torch.Tensor, ori: torch.Tensor) -> float:
+    """Relative L1 drift of `new` against `ori` over the positions where neither is NaN:
+    mean|new - ori| / (mean|ori| + 1e-8); mean|new| when mean|ori| < 1e-6; inf when no position is
+    valid or the result is not finite.  fp64 accumulation."""
+    valid = ~(torch.isnan(new) | torch.isnan(ori))
+    if not bool(valid.any()):
+        return float("inf")
+    n, o = new[valid].double(), ori[valid].double()
+    ori_mean = o.abs().mean().item()
+    if ori_mean < 1e-6:
+        return n.abs().mean().item()
+    val = (n - o).abs().mean().item() / (ori_mean + 1e-8)
+    return val if math.isfinite(val) else float("inf")
 
 
 # --------------------------------------------------------------------------------------

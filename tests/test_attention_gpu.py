@@ -125,3 +125,24 @@ def test_packed_ring_two_gpus():
         for t in range(5):
             e = (ret[r][0][t][0, :valid] - ref[t][r][:valid]).abs()
             assert e.max() <= 2e-2 and e.mean() <= 1e-3
+
+
+def test_profiling_mode_records_drift_on_device():
+    """RedundancyMap in profiling mode: full stride everywhere, drift of consecutive outputs added
+    to the map by the device kernel, equal to the reference's rel_l1 of those outputs."""
+    from ditango_b200.core import redundancy_map as rmod
+    from ditango_b200.utils import update_timestep
+    layer = _single_layer(3)
+    rm = rmod.get_redundancy_map()
+    rm.enable_auto_setting()
+    data = O.drifting_qkv(1, 700, 2, 64, 3, seed=5, dtype=torch.bfloat16)
+    outs = []
+    for t, (q, k, v) in enumerate(data):
+        update_timestep(t)
+        outs.append(layer.attn(q.cuda(), k.cuda(), v.cuda()).cpu())
+    rm.finish_auto_setting()
+    assert rm.redundancy_map[0, 0] == 0
+    for t in (1, 2):
+        want = O.rel_l1(outs[t], outs[t - 1])
+        assert abs(rm.redundancy_map[t, 0].item() - want) <= 1e-5 * max(1.0, want)
+    assert not rm.is_auto_setting()

@@ -191,3 +191,39 @@ def test_rejected_arguments_raise():
         ops.flash_partial(q.float(), q.float(), q.float())
     with pytest.raises(ExtensionError):
         ops.flash_partial(q.cpu(), q.cpu(), q.cpu())
+
+
+@pytest.mark.parametrize("n", [1, 1000, 16384, 16385, 3_200_003])
+def test_drift_accumulate_matches_reference_metric(n):
+    ops = _ops()
+    g = torch.Generator().manual_seed(n)
+    prev = torch.randn(n, generator=g)
+    cur = prev + 0.05 * torch.randn(n, generator=g)
+    if n > 10:
+        cur[3] = float("nan")
+        prev[7] = float("nan")
+    want = O.rel_l1(cur, prev)
+    acc = torch.zeros(2, device="cuda")
+    ops.drift_accumulate(cur.cuda(), prev.cuda(), acc[1:])
+    ops.drift_accumulate(cur.cuda(), prev.cuda(), acc[1:])          # accumulates; scratch is reusable
+    got = acc.cpu()
+    assert got[0] == 0
+    assert abs(got[1].item() - 2 * want) <= 2e-6 * max(1.0, abs(2 * want))
+
+
+def test_drift_accumulate_special_cases():
+    ops = _ops()
+    n = 5000
+    prev = torch.full((n,), 1e-9)
+    cur = torch.randn(n, generator=torch.Generator().manual_seed(1))
+    acc = torch.zeros(1, device="cuda")
+    ops.drift_accumulate(cur.cuda(), prev.cuda(), acc)              # reference magnitude too small -> mean|cur|
+    assert abs(acc.item() - O.rel_l1(cur, prev)) < 1e-6
+    acc.zero_()
+    ops.drift_accumulate(torch.full((n,), float("nan")).cuda(), prev.cuda(), acc)
+    assert math.isinf(acc.item()) and O.rel_l1(torch.full((n,), float("nan")), prev) == float("inf")
+    # an odd (4-byte aligned only) view takes the scalar path
+    base = torch.randn(n + 1, generator=torch.Generator().manual_seed(2))
+    acc.zero_()
+    ops.drift_accumulate(base.cuda()[1:], (base * 1.1).cuda()[1:], acc)
+    assert abs(acc.item() - O.rel_l1(base[1:], (base * 1.1)[1:])) < 1e-6
