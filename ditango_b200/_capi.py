@@ -20,6 +20,7 @@ EXPORTS = (
     "dtb_version", "dtb_last_error", "dtb_device_supported", "dtb_read_status",
     "dtb_flash_fwd", "dtb_merge_states", "dtb_copy_chunks",
     "dtb_drift_scratch_bytes", "dtb_drift_accumulate",
+    "dtb_drift_noalloc_max_elements", "dtb_drift_accumulate_noalloc",
 )
 
 
@@ -64,6 +65,9 @@ def load():
     lib.dtb_drift_scratch_bytes.argtypes = [c_int64]
     lib.dtb_drift_accumulate.restype = c_int
     lib.dtb_drift_accumulate.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]
+    lib.dtb_drift_noalloc_max_elements.restype = c_int64
+    lib.dtb_drift_accumulate_noalloc.restype = c_int
+    lib.dtb_drift_accumulate_noalloc.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
     _lib = lib
     return lib
 

@@ -4,6 +4,7 @@
 
 #include "flash_fwd_sm100.cuh"
 #include "drift_stats.cuh"
+#include "errors.cuh"
 #include "merge_states.cuh"
 
 #include <cuda.h>
@@ -61,6 +62,27 @@ int device_info(DeviceInfo** out) {
   *out = &d;
   return DTB_OK;
 }
+
+}  // namespace
+
+namespace dtb {
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int require_sm100() {
+  DeviceInfo* d = nullptr;
+  return device_info(&d);
+}
+
+}  // namespace dtb
+
+namespace {
 
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 

@@ -8,6 +8,11 @@
 // blocks x 4 doubles {sum|cur-prev|, sum|prev|, sum|cur|, count}.
 #include "drift_stats.cuh"
 
+#include "../../include/ditango_b200.h"
+#include "errors.cuh"
+
+#include <mutex>
+
 #include <math.h>
 
 namespace dtb {
@@ -116,3 +121,71 @@ cudaError_t launch_drift_stats(const float* cur, const float* prev, int64_t n, f
 }
 
 }  // namespace dtb
+
+// ------------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate: the scratch lives in this library's own device image.
+//
+// Some hosts of this library cannot give it memory at call time: an inference server that hands its
+// whole device budget to its own pool at start-up and forbids later cudaMalloc (which would also
+// stall every stream of the process while it runs), or a plug-in interface that passes inputs and
+// outputs only.  For them the per-block partial sums go into a fixed array that every process
+// loading the library carries on each GPU it uses, from load until exit (1 MiB).
+namespace {
+
+constexpr int64_t kStaticBlocks = 32760;                                           // 1 MiB in all
+constexpr int64_t kStaticBytes = dtb::kDriftScratchHeader + kStaticBlocks * 4 * 8;
+static_assert(kStaticBytes == (1 << 20), "static drift scratch is meant to be exactly 1 MiB");
+
+static __device__ __align__(256) unsigned char g_drift_static_scratch[kStaticBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address: the address
+// is looked up once per device, with that device current, and kept here.
+unsigned char* g_static_ptr[64] = {};
+std::mutex g_static_mu;
+
+int static_scratch(unsigned char** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return dtb::set_error(DTB_ERR_CUDA, "dtb_drift_accumulate_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_drift_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return dtb::set_error(DTB_ERR_CUDA, "dtb_drift_accumulate_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return DTB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+DTB_API int64_t dtb_drift_noalloc_max_elements(void) { return kStaticBlocks * dtb::kDriftTile; }
+
+DTB_API int dtb_drift_accumulate_noalloc(const float* cur, const float* prev, int64_t n, float* accum, void* stream) {
+  if (n < 0) return dtb::set_error(DTB_ERR_ARG, "dtb_drift_accumulate_noalloc: negative length");
+  if (!accum || (n > 0 && (!cur || !prev))) return dtb::set_error(DTB_ERR_ARG, "dtb_drift_accumulate_noalloc: null pointer");
+  if (dtb::drift_blocks(n) > kStaticBlocks)
+    return dtb::set_error(DTB_ERR_ARG,
+                          "dtb_drift_accumulate_noalloc: n = %lld exceeds the %lld elements the built-in scratch covers; "
+                          "use dtb_drift_accumulate with caller-provided scratch",
+                          static_cast<long long>(n), static_cast<long long>(kStaticBlocks * dtb::kDriftTile));
+  int rc = dtb::require_sm100();
+  if (rc != DTB_OK) return rc;
+  unsigned char* scratch = nullptr;
+  rc = static_scratch(&scratch);
+  if (rc != DTB_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Only the ticket counter has to start at zero
+  // (a call that ran to completion leaves it so; this also covers one that did not).
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(unsigned int), s);
+  if (e == cudaSuccess) e = dtb::launch_drift_stats(cur, prev, n, accum, scratch, s);
+  if (e != cudaSuccess) return dtb::set_error(DTB_ERR_CUDA, "dtb_drift_accumulate_noalloc failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
+}  // extern "C"

@@ -141,6 +141,23 @@ DTB_API int64_t dtb_drift_scratch_bytes(int64_t n);
 DTB_API int dtb_drift_accumulate(const float* cur, const float* prev, int64_t n, float* accum,
                                  void* scratch, int64_t scratch_bytes, void* stream);
 
+/*
+ * dtb_drift_accumulate for callers that cannot supply (or allocate) scratch memory.  It has no
+ * counterpart in the reference.  Same result as dtb_drift_accumulate; the partial sums go into a
+ * 1 MiB array built into the library's device image, which every GPU that loads the library holds
+ * until the process exits.  No cudaMalloc / cudaFree or allocating library routine is called.
+ *
+ *  - n is limited to dtb_drift_noalloc_max_elements() (536,739,840); larger inputs are rejected
+ *    with DTB_ERR_ARG and a message naming the limit.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and remembers it; make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's contents; the
+ *    entry point clears the one word that must start at zero.  Two calls that overlap on the GPU
+ *    (different streams, or different host threads) race on it: serialise them.
+ */
+DTB_API int64_t dtb_drift_noalloc_max_elements(void);
+DTB_API int dtb_drift_accumulate_noalloc(const float* cur, const float* prev, int64_t n, float* accum, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
