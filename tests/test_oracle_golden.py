@@ -11,7 +11,7 @@ import torch
 from oracle import ring_oracle as O
 
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
-CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")))
+CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")) if not p.endswith("schedules.npz"))
 TOL = 2e-5
 
 
