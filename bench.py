@@ -403,6 +403,96 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_dit(args):
+    """BASELINE config 5: random-init CogVideoX-5B-shaped DiT (42 layers, hidden 3072, 48 x 64 heads),
+    latent 13x60x90x16 + 226 text tokens, classifier-free guidance in-batch (B = 2), bf16; one step =
+    one denoising step of the whole model.  Prints ms per step and exposed communication."""
+    import torch.distributed as dist
+    from ditango_b200 import _capi, ops
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core.group_coordinate import SingleRankGroup
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.executor.cogvideox_dit import CogVideoXDiT, DiTConfig, denoise
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _capi.check(_capi.load().dtb_device_supported(), "dtb_device_supported")
+    dcfg = DiTConfig()
+    if args.layers:
+        dcfg.num_layers = args.layers
+    steps_total = 50
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = dcfg.num_layers, steps_total
+    cfg.use_ditango, cfg.use_ulysses = args.mode == "ditango", args.mode == "ulysses"
+    if world > 1:
+        ps.init_distributed_environment(world_size=world, rank=rank, local_rank=local_rank, backend="nccl")
+        c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+        ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+        group = ps.get_isp_group()
+    else:
+        group = SingleRankGroup(device)
+    rm = init_redundancy_map(cfg, world_size=world)
+    if args.mode == "ditango" and world > 1:
+        rm.divider_map = torch.from_numpy(draw_dividers(steps_total, dcfg.num_layers, world, 0.6))
+        rm._refine_divider_map()
+        rm.screen_self_sends()
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = CogVideoXDiT(dcfg, group, mode=args.mode).to(torch.bfloat16)
+    g = torch.Generator(device=device).manual_seed(0)
+    latents = torch.randn(1, dcfg.frames, dcfg.in_channels, dcfg.height, dcfg.width, generator=g, device=device,
+                          dtype=torch.float32).to(torch.bfloat16)
+    text_c = torch.randn(1, dcfg.text_len, dcfg.text_dim, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    text_u = torch.randn(1, dcfg.text_len, dcfg.text_dim, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    layers = [b.attention for b in model.blocks if b.attention is not None]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    latents = denoise(model, latents, text_c, text_u, num_steps=args.warmup, first_step=0)
+    barrier()
+    for L in layers:
+        L.measure_comm = world > 1
+        L.exposed_comm_ms()
+    ops.LaunchLog.reset(with_events=True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    latents = denoise(model, latents, text_c, text_u, num_steps=args.steps, first_step=args.warmup)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    flash_ms = sum(a.elapsed_time(b) for a, b, _ in ops.LaunchLog.events)
+    flash_flops = sum(f for _, _, f in ops.LaunchLog.events)
+    n_flash = len(ops.LaunchLog.events)
+    launches = ops.LaunchLog.count
+    exposed = sum(L.exposed_comm_ms() for L in layers)
+    status = ops.read_status()
+    stats = torch.tensor([ms, exposed, flash_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, exposed, flash_ms = stats.tolist()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ms per denoising step, random-init CogVideoX-5B-shaped DiT", "value": round(ms / args.steps, 3),
+            "unit": "ms/step", "higher_is_better": False, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16", "data": "synthetic", "scaling": "strong",
+            "config": {"workload": f"cogvideox-dit: {dcfg.num_layers} layers, hidden {dcfg.dim}, {dcfg.num_heads}x{dcfg.head_dim} heads, "
+                                   f"{dcfg.video_tokens}+{dcfg.text_len} tokens, CFG batch 2, mode={args.mode}", "mode": args.mode},
+            "exposed_comm_ms_per_step": round(exposed / args.steps, 3),
+            "attention_kernel_ms_per_step": round(flash_ms / args.steps, 3),
+            "attention_kernel_tflops": round(flash_flops / max(flash_ms, 1e-9) / 1e9, 1),
+            "flash_launches": n_flash, "gpu_launches": launches, "kernel_status": status,
+            "finite": bool(torch.isfinite(latents.float()).all().item())}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_micro(args):
     """Single-kernel timing on one GPU (also the small case the ncu captures under profiles/ use):
     one chunk pair of the workload at S/shard tokens (`flash`), an n-state merge at that shape
@@ -458,7 +548,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="hunyuan", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="hunyuan", choices=sorted(WORKLOADS) + ["cogvideox-dit"])
     ap.add_argument("--mode", default="ditango", choices=["ditango", "ring", "ulysses"])
     ap.add_argument("--layers", type=int, default=0, help="override layers per step (debugging only)")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
@@ -469,6 +559,8 @@ def main():
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)
+    if args.workload == "cogvideox-dit":
+        return run_dit(args)
     if args.warmup < 3 and args.impl == "ours":
         print("warning: fewer than 3 warm-up steps", file=sys.stderr)
     if args.impl == "reference":

@@ -139,3 +139,26 @@ def gpu_ring_worker(rank, world, port, case, ret):
     ret[rank] = (torch.stack(outs), dict(layer.stats), uly, status)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def dit_worker(rank, world, port, mode, ret):
+    """Tiny CogVideoX-shaped DiT on gloo ranks with the CPU engine: output must not depend on the
+    number of ranks the sequence is sharded over."""
+    cfg_, ps = _setup(rank, world, port)
+    from tests import cpu_engine
+    import ditango_b200.executor.cogvideox_dit as M
+    M._engine = cpu_engine
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    cfg_.num_layers, cfg_.num_inference_steps = 2, 3
+    init_redundancy_map(cfg_)
+    dcfg = M.DiTConfig(num_layers=2, num_heads=4, head_dim=16, in_channels=4, patch_size=2, text_dim=32, time_dim=16,
+                       frames=2, height=8, width=8, text_len=8)
+    torch.manual_seed(0)
+    model = M.CogVideoXDiT(dcfg, ps.get_isp_group(), mode=mode)
+    g = torch.Generator().manual_seed(1)
+    lat = torch.randn(1, 2, 4, 8, 8, generator=g)
+    txt_c, txt_u = torch.randn(1, 8, 32, generator=g), torch.randn(1, 8, 32, generator=g)
+    out = M.denoise(model, lat, txt_c, txt_u, num_steps=2)
+    ret[rank] = out
+    dist.barrier()
+    dist.destroy_process_group()
