@@ -12,8 +12,9 @@ What is different underneath:
     reference, called at core/attention.py:144, :193-196);
   * cached blocks, the own chunk and the fresh block are combined by one N-way merge launch
     (reference: a chain of pairwise merges at :110-116 and :213);
-  * KV chunks go owner -> consumer directly, K and V (and cu_seqlens) of a hop in one NCCL group,
-    received into two persistent slots that alternate; no clone before a send (reference: :51);
+  * KV chunks go owner -> consumer directly, K and V (and cu_seqlens) of a hop in one NCCL group; all
+    hops of a call are posted up front into persistent per-hop slots and each is waited for just
+    before the launch that reads it; no clone before a send (reference: :51);
   * the first-KV exchange is decided at block level; the reference decides it at chunk level
     (:120), which makes it address itself and count its own chunk twice after some stride
     transitions.  On schedules without such self-sends both give the same result.
@@ -35,16 +36,16 @@ from .schedule import StepPlan, plan_step
 
 logger = init_logger(__name__)
 
-# Two alternating receive slots per (device, shape, dtype), shared by all layers of the process:
-# layers run one after another, so one pair is enough.
-_SLOTS: Dict[Tuple, List[torch.Tensor]] = {}
+# One receive slot per hop and (device, shape, dtype), shared by all layers of the process: layers run
+# one after another, and a layer call has at most group-size hops in flight.
+_SLOTS: Dict[Tuple, torch.Tensor] = {}
 
 
 def _slot(tag: str, index: int, like: torch.Tensor) -> torch.Tensor:
-    key = (tag, like.device, tuple(like.shape), like.dtype)
+    key = (tag, index, like.device, tuple(like.shape), like.dtype)
     if key not in _SLOTS:
-        _SLOTS[key] = [torch.empty_like(like, memory_format=torch.contiguous_format) for _ in range(2)]
-    return _SLOTS[key][index]
+        _SLOTS[key] = torch.empty_like(like, memory_format=torch.contiguous_format)
+    return _SLOTS[key]
 
 
 def release_receive_slots():
@@ -73,8 +74,9 @@ class proAttention:
         self._comm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
 
     # ------------------------------------------------------------------ transport
-    def _commit_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
-        """Post this rank's sends of its own chunk and its receive for `hop` as one batch."""
+    def _post_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
+        """Post this rank's sends of its own chunk and its receive for `hop` as one batch of its own.
+        Returns (received tensors or None, batch handle)."""
         me = self.local_chunk_id
         src = plan.recv_from(me, hop)
         recv = None
@@ -82,21 +84,20 @@ class proAttention:
             for t in payload:
                 self.group.p2p_isend(t, dst=dst)
         if src is not None:
-            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(f"kv{i}", hop & 1, t)) for i, t in enumerate(payload))
+            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(f"kv{i}", hop, t)) for i, t in enumerate(payload))
             self.stats["chunks_received"] += 1
             self.stats["bytes_received"] += sum(t.numel() * t.element_size() for t in payload)
-        self.group.p2p_commit()
-        return recv
+        return recv, self.group.p2p_commit_batch()
 
-    def _wait_hop(self):
+    def _wait_hop(self, handle):
         if self.measure_comm and torch.cuda.is_available():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            self.group.p2p_wait()
+            self.group.p2p_wait_batch(handle)
             b.record()
             self._comm_events.append((a, b))
         else:
-            self.group.p2p_wait()
+            self.group.p2p_wait_batch(handle)
 
     def exposed_comm_ms(self, reset: bool = True) -> float:
         """Time the compute stream spent blocked on incoming KV since the last reset."""
@@ -153,21 +154,20 @@ class proAttention:
                     states.append((o, l, LSE_BHS))
             self.stats["cached_blocks_merged"] += len(states)
 
-        # 2. own chunk first when the target block is a foreign one; its flash overlaps hop 0
+        # 2. every hop of this call is posted now, each as its own batch into its own slot: chunks
+        #    travel owner -> consumer, so the hops do not depend on one another and the link streams
+        #    them back to back while the attention kernels work through the chunks already here.
+        posted = [self._post_hop(plan, hop, payload) for hop in range(stride)] if N > 1 else [(None, None)] * stride
         own = None
-        incoming = None
         if mine.own_first:
-            incoming = self._commit_hop(plan, 0, payload)
-            own = attend(payload)
-            self._wait_hop()
+            own = attend(payload)          # target block is a foreign one: own chunk first, overlapping hop 0
 
         # 3. the target block's chunks
         fresh = None
         chunk_states = []
         for hop in range(stride):
-            current = payload if mine.owners[hop] == me else incoming
-            if hop + 1 < stride:
-                incoming = self._commit_hop(plan, hop + 1, payload)
+            current, handle = posted[hop]
+            self._wait_hop(handle)
             if mine.owners[hop] == me:
                 own = attend(payload)
             elif keep_chunks:
@@ -178,8 +178,6 @@ class proAttention:
                 fresh = attend(current, into=fresh)
             else:
                 own = attend(current, into=own)          # nothing is kept: fold into the result
-            if hop + 1 < stride:
-                self._wait_hop()
 
         # 4. store the fresh block, combine everything in one pass
         if fresh is not None:

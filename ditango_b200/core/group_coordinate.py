@@ -132,6 +132,19 @@ class GroupCoordinator:
         self.p2p_ops.clear()
         self.p2p_reqs = None
 
+    # Several batches in flight at once (not in the reference): every hop of a layer call is posted
+    # up front as its own batch and waited for just before the attention launch that consumes it.
+    def p2p_commit_batch(self):
+        """Launch the queued operations as one batch and return its handle; other batches may be in flight."""
+        reqs = dist.batch_isend_irecv(self.p2p_ops) if self.p2p_ops else []
+        self.p2p_ops = []
+        return reqs
+
+    @staticmethod
+    def p2p_wait_batch(reqs):
+        for req in reqs or []:
+            req.wait()
+
     def destroy(self):
         for g in (self.device_group, self.cpu_group):
             if g is not None:
@@ -162,3 +175,10 @@ class SingleRankGroup:
 
     def barrier(self):
         pass
+
+    def p2p_commit_batch(self):
+        return []
+
+    @staticmethod
+    def p2p_wait_batch(reqs):
+        return None
