@@ -352,7 +352,7 @@ def cpu_baseline(w, world, sample_seq=None, steps=1, min_seconds=0.0):
     cores = os.cpu_count() or 1
     torch.set_num_threads(max(1, cores // world))
     B, H, D = w["B"], w["H"], w["D"]
-    s_loc = sample_seq or 4096
+    s_loc = max(256, (sample_seq or 4096) // world)      # the sample keeps ~sample_seq tokens in all
     S = s_loc * world
     data = O.drifting_qkv(B, S, H, D, 1, seed=0, dtype=torch.bfloat16, rms_norm_qk=w["rms"])
     t0 = time.perf_counter()

@@ -1,8 +1,8 @@
 """Generate tests/golden/*.npz by EXECUTING THE REFERENCE on CPU/gloo ranks.
 
-Run in a container that has the reference checked out (default /root/reference):
+Run where the reference (chen-yy20/ditango) is checked out:
 
-    python tests/golden/make_golden.py [--ref /path/to/reference]
+    python tests/golden/make_golden.py --ref /path/to/reference
 
 The reference's per-layer attention object (`proAttention.attn` / `.varlen_attn`) is driven
 unmodified; only what cannot exist on a CPU box is shimmed:
@@ -154,7 +154,8 @@ CASES = {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("DITANGO_REFERENCE", "reference"),
+                    help="checkout of chen-yy20/ditango")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     refpkg = tempfile.mkdtemp(prefix="ditango_refpkg_")

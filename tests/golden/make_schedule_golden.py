@@ -23,7 +23,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("DITANGO_REFERENCE", "reference"),
+                    help="checkout of chen-yy20/ditango")
     args = ap.parse_args()
     m, mpp = types.ModuleType("matplotlib"), types.ModuleType("matplotlib.pyplot")
     m.pyplot = mpp
