@@ -55,6 +55,15 @@ def measured_peaks():
     return dict(tensor=1400.0, tensor_burst=1590.0, hbm=6650.0, source="fallback")
 
 
+def flash_dram_traffic(B, S_q, H, D):
+    """DRAM bytes of one flash launch on a square chunk pair, scaled from the ncu captures under
+    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): 429.7 MB at B1 S14882 H24 D128 and
+    519.0 MB at B2 S8888 H48 D64.  K and V of a head stay in L2 while its query tiles run, so traffic
+    follows the tensor sizes (tokens x heads x head_dim), not the FLOPs."""
+    ref = {128: (429.7e6, 1 * 14882 * 24 * 128), 64: (519.0e6, 2 * 8888 * 48 * 64)}[D]
+    return ref[0] * (B * S_q * H * D) / ref[1]
+
+
 def draw_dividers(steps, layers, world, p, seed=0):
     """Bernoulli(p) reuse per (step, layer); a reuse cell takes a divider drawn uniformly from
     {2,4,8} that divides the group size; step 0 is a full refresh."""
@@ -328,7 +337,8 @@ def run_ours(args):
                          "unit": "TFLOP/s", "frac": round(per_launch_tflops / peaks["tensor"], 4),
                          "peak_kind": f"{peaks['source']} sustained bf16 cuBLAS GEMM; burst {peaks['tensor_burst']}",
                          "kernel": f"flash_fwd_kernel<{D}>", "launches_timed": int(n_flash),
-                         "traffic": None},
+                         "traffic": round(flash_dram_traffic(B, S_loc, H, D)),
+                         "traffic_kind": "bytes per launch, scaled by tensor size from the ncu capture of a smaller chunk pair"},
             "clocks": clocks,
             "e2e": {"value": round(tot_e2e_flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                     "ms_per_step": round(e2e_ms / e2e_steps, 3),
