@@ -78,6 +78,24 @@ def draw_dividers(steps, layers, world, p, seed=0):
     return div
 
 
+def draw_pair_map(workload, steps, layers, world, p, seed=0):
+    """Per-pair reuse map reusable[t, l, src, dst] as BASELINE words it: Bernoulli(p) per (step, layer,
+    source chunk, consumer) with step 0 all-fresh; for stepvideo the structured map "chunks more than
+    two ring hops away are reusable after step 10"."""
+    r = np.zeros((steps, layers, world, world), dtype=bool)
+    if workload == "stepvideo":
+        for src in range(world):
+            for dst in range(world):
+                if min((src - dst) % world, (dst - src) % world) > 2:
+                    r[11:, :, src, dst] = True
+    else:
+        r = np.random.RandomState(seed).rand(steps, layers, world, world) < p
+        r[0] = False
+    for i in range(world):
+        r[:, :, i, i] = False
+    return r
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -178,7 +196,9 @@ def run_ours(args):
         group = SingleRankGroup(device)
     rm = init_redundancy_map(cfg, world_size=world)
     reuse_cells = 0
-    if args.mode == "ditango" and world > 1:
+    if args.mode == "ditango" and world > 1 and args.schedule == "pairs":
+        rm.set_pair_map(draw_pair_map(args.workload, w["steps"], w["layers"], world, w["p"]))
+    elif args.mode == "ditango" and world > 1:
         rm.divider_map = torch.from_numpy(draw_dividers(w["steps"], w["layers"], world, w["p"]))
         rm._refine_divider_map()
         rm.screen_self_sends()
@@ -329,7 +349,8 @@ def run_ours(args):
                                    f"mode={args.mode}, sequence sharded over {world} rank(s)",
                        "mode": args.mode, "global_batch": B, "seq_len": S, "layers_per_step": w["layers"],
                        "l2": "inputs larger than L2 (Q,K,V of one layer call exceed 126 MB)",
-                       "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0},
+                       "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0,
+                       "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none"},
             "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
             "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
             "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
@@ -561,6 +582,8 @@ def main():
     ap.add_argument("--workload", default="hunyuan", choices=sorted(WORKLOADS) + ["cogvideox-dit"])
     ap.add_argument("--mode", default="ditango", choices=["ditango", "ring", "ulysses"])
     ap.add_argument("--layers", type=int, default=0, help="override layers per step (debugging only)")
+    ap.add_argument("--schedule", default="stride", choices=["stride", "pairs"],
+                    help="ditango mode: stride schedule (what the reference can express) or a per-pair reuse map")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy"], help="time one kernel and exit")

@@ -32,7 +32,7 @@ from ..utils import get_timestep
 from .cache import proCache
 from .config import get_config
 from .redundancy_map import get_redundancy_map
-from .schedule import StepPlan, plan_step
+from .schedule import StepPlan, plan_pair_step, plan_step
 
 logger = init_logger(__name__)
 
@@ -68,6 +68,10 @@ class proAttention:
         self.small_ring_stride = 8
         self.measure_memory = False
         self.measure_comm = False
+        # per-pair reuse maps (RedundancyMap.set_pair_map): cached state per source chunk, and which
+        # chunks every rank of the group holds (all ranks keep the same copy)
+        self._chunk_states: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._have = [set() for _ in range(self.isp_size)]
         self.last_lse: Optional[torch.Tensor] = None       # [B,H,S] / [H,T] of the last result
         self.stats = dict(calls=0, chunks_attended=0, chunks_received=0, bytes_received=0,
                           cached_blocks_merged=0, merge_launches=0)
@@ -109,11 +113,50 @@ class proAttention:
             self._comm_events = []
         return total
 
+    # ------------------------------------------------------------------ per-pair reuse (extension)
+    def _run_pairs(self, flags, query, key, value, cu_q=None, cu_kv=None, max_q=None, max_kv=None):
+        """One call under a per-pair reuse map: own chunk always fresh; every other chunk either from
+        this rank's per-chunk cache or fetched from its owner and recomputed, as flags[src][me] says."""
+        N, me = self.isp_size, self.local_chunk_id
+        packed = cu_q is not None
+        payload = (key, value, cu_kv) if packed else (key, value)
+
+        def attend(kv):
+            kw = {}
+            if packed:
+                kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
+            self.stats["chunks_attended"] += 1
+            return _engine.flash_partial(query, kv[0], kv[1], lse_layout=LSE_BHS, **kw)
+
+        plan = plan_pair_step(N, flags, self._have)
+        posted = [self._post_hop(plan, hop, payload) for hop in range(plan.n_hops)]
+        own = attend(payload)
+        for hop in range(plan.n_hops):
+            current, handle = posted[hop]
+            self._wait_hop(handle)
+            if current is not None:
+                self._chunk_states[plan.ranks[me].owners[hop]] = attend(current)
+        others = [(o, l, LSE_BHS) for src in ((me + i) % N for i in range(1, N))
+                  for o, l in (self._chunk_states.get(src, (None, None)),) if l is not None]
+        self.stats["cached_blocks_merged"] += len(others) - len(plan.ranks[me].owners)
+        if others:
+            out, lse = _engine.merge_states([(own[0], own[1], LSE_BHS)] + others, out=own[0], lse_out=own[1],
+                                            lse_out_layout=LSE_BHS)
+            self.stats["merge_launches"] += 1
+        else:
+            out, lse = own
+        self.last_lse = lse
+        self.stats["calls"] += 1
+        return out
+
     # ------------------------------------------------------------------ the call
     def _run(self, query, key, value, cu_q=None, cu_kv=None, max_q=None, max_kv=None):
         N, me = self.isp_size, self.local_chunk_id
         rmap = get_redundancy_map()
         t = get_timestep()
+        flags = rmap.pair_flags(t, self.layer_id) if N > 1 else None
+        if flags is not None:
+            return self._run_pairs(flags, query, key, value, cu_q, cu_kv, max_q, max_kv)
         stride = rmap.get_curr_isp_stride(t, self.layer_id)
         next_stride = rmap.get_next_isp_stride(t, self.layer_id)
         if t == 0:

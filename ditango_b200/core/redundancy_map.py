@@ -53,6 +53,29 @@ class RedundancyMap:
     def _init_map(self) -> torch.Tensor:
         return torch.ones(self.num_timesteps, self.num_layers, dtype=torch.long)
 
+    # ------------------------------------------------------------------ per-pair reuse (extension)
+    def set_pair_map(self, reusable):
+        """Switch the schedule to a per-pair reuse map reusable[t, l, src, dst] (bool array-like,
+        [steps, layers, N, N]) or back to the stride schedule (None).  The reference has no such map:
+        its (src, dst) pattern always follows from a stride and a rotating pointer.  With a pair map set,
+        every attention object keeps one cached state per source chunk and refreshes exactly the pairs
+        that are not flagged (or were never computed)."""
+        if reusable is None:
+            self.pair_reuse = None
+            return
+        arr = np.asarray(reusable, dtype=bool)
+        N = self.base_weight
+        assert arr.shape == (self.num_timesteps, self.num_layers, N, N), \
+            f"pair map must be [steps, layers, {N}, {N}], got {arr.shape}"
+        self.pair_reuse = arr
+
+    def pair_flags(self, timestep: int, layer_id: int):
+        """reusable[src][dst] of one cell as nested lists, or None when the stride schedule is active."""
+        pr = getattr(self, "pair_reuse", None)
+        if pr is None or self.auto_setting:
+            return None
+        return pr[timestep, layer_id].tolist()
+
     def _dividers(self) -> List[List[int]]:
         if self._table is None:
             self._table = self._divider_map.tolist()

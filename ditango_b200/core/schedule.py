@@ -26,12 +26,18 @@ class StepPlan:
     ranks: List[RankPlan]
     pointers_after: List[int]
 
+    @property
+    def n_hops(self) -> int:
+        return max(len(p.owners) for p in self.ranks)
+
     def recv_from(self, rank: int, hop: int) -> Optional[int]:
-        o = self.ranks[rank].owners[hop]
-        return None if o == rank else o
+        owners = self.ranks[rank].owners
+        if hop >= len(owners) or owners[hop] == rank:
+            return None
+        return owners[hop]
 
     def send_to(self, rank: int, hop: int) -> List[int]:
-        return [r for r, p in enumerate(self.ranks) if r != rank and p.owners[hop] == rank]
+        return [r for r, p in enumerate(self.ranks) if r != rank and hop < len(p.owners) and p.owners[hop] == rank]
 
 
 def plan_step(world: int, stride: int, pointers: List[int]) -> StepPlan:
@@ -46,3 +52,25 @@ def plan_step(world: int, stride: int, pointers: List[int]) -> StepPlan:
         plans.append(RankPlan(target_block=tb, local_block=lb, own_first=(tb != lb), owners=owners))
         after.append((ptr + (world if stride == world else stride)) % world)
     return StepPlan(stride=stride, ranks=plans, pointers_after=after)
+
+
+def plan_pair_step(world: int, reusable, have: List[set]) -> StepPlan:
+    """Planning for a per-pair reuse map (an extension; the reference cannot express it).
+
+    reusable[src][dst]: consumer `dst` may take chunk `src` from its cache this step; have[dst]: the
+    chunks `dst` holds a cached state for.  A pair is fetched and recomputed when it is not flagged, or
+    flagged but never computed.  Each consumer walks the other chunks in ring order (dst+1, dst+2, ...);
+    its h-th fetch is hop h.  `have` is updated in place.  A hop is no longer a permutation: a rank may
+    serve several consumers in one hop, and ranks need different numbers of hops.
+    """
+    plans = []
+    for dst in range(world):
+        fetch = []
+        for step in range(1, world):
+            src = (dst + step) % world
+            if not (reusable[src][dst] and src in have[dst]):
+                fetch.append(src)
+        plans.append(RankPlan(target_block=-1, local_block=-1, own_first=True, owners=fetch))
+    for dst, p in enumerate(plans):
+        have[dst].update(p.owners)
+    return StepPlan(stride=0, ranks=plans, pointers_after=[])

@@ -471,6 +471,58 @@ def run_ring_group(world: int, dividers_col: Sequence[int],
 
 
 # --------------------------------------------------------------------------------------
+# Generalised per-chunk reuse (pair maps).  NOT in the reference: its schedule can only express
+# pair maps that follow from a stride and a rotating pointer.  Here every (source chunk, consumer
+# rank) pair carries its own flag per step: a flagged pair takes the partial state the consumer
+# computed for that chunk the last time it was fresh; an unflagged pair -- or a flagged one that
+# was never computed -- is recomputed from the current step's tensors.  On pair maps expanded from
+# a stride schedule this gives the reference's result up to fp32 rounding (tested).
+# --------------------------------------------------------------------------------------
+
+def run_pair_map_group(world: int, reusable: np.ndarray,
+                       qkv_per_step: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]],
+                       partial_dtype: Optional[torch.dtype] = None) -> List[List[torch.Tensor]]:
+    """reusable[t, src, dst] bool; qkv_per_step[t] = global (q, k, v) [B,S,H,D].  Returns outs[t][dst]
+    (fp32 [B,S_loc,H,D]): own chunk first, then the other chunks in ring order (dst+1, dst+2, ...)."""
+    T = len(qkv_per_step)
+    cache: List[Dict[int, Tuple[torch.Tensor, torch.Tensor]]] = [dict() for _ in range(world)]
+    outs: List[List[torch.Tensor]] = []
+    for t in range(T):
+        q, k, v = qkv_per_step[t]
+        S = q.shape[1]
+        sl = [slice(r * S // world, (r + 1) * S // world) for r in range(world)]
+        row = []
+        for dst in range(world):
+            ql = q[:, sl[dst]]
+            o, l = partial_attention(ql, k[:, sl[dst]], v[:, sl[dst]], out_dtype=partial_dtype)
+            out, lse = merge_states(None, None, o, l)
+            for step in range(1, world):
+                src = (dst + step) % world
+                if not (bool(reusable[t, src, dst]) and src in cache[dst]):
+                    o, l = partial_attention(ql, k[:, sl[src]], v[:, sl[src]], out_dtype=partial_dtype)
+                    cache[dst][src] = (o.float(), l)
+                co, cl = cache[dst][src]
+                out, lse = merge_states(out, lse, co, cl)
+            row.append(out)
+        outs.append(row)
+    return outs
+
+
+def pair_map_from_dividers(dividers_col: Sequence[int], world: int) -> np.ndarray:
+    """The reusable[t, src, dst] view of one layer's stride schedule (pointer replay)."""
+    tr = replay_pointers(dividers_col, world)
+    out = np.zeros((len(tr), world, world), dtype=bool)
+    for t, rec in enumerate(tr):
+        s = rec["stride"]
+        if s == world:
+            continue
+        for dst in range(world):
+            for src in range(world):
+                out[t, src, dst] = src != dst and src // s != rec["target_block"][dst]
+    return out
+
+
+# --------------------------------------------------------------------------------------
 # Ulysses (baseline/ulysses.py:51-124)
 # --------------------------------------------------------------------------------------
 

@@ -162,3 +162,65 @@ def dit_worker(rank, world, port, mode, ret):
     ret[rank] = out
     dist.barrier()
     dist.destroy_process_group()
+
+
+def pair_worker(rank, world, port, case, ret):
+    """proAttention under a per-pair reuse map on gloo ranks (CPU engine)."""
+    cfg, ps = _setup(rank, world, port)
+    import numpy as np
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.utils import update_timestep
+    from oracle.ring_oracle import drifting_qkv
+    T = case["T"]
+    cfg.num_layers, cfg.num_inference_steps = 1, T
+    rm = init_redundancy_map(cfg)
+    rm.set_pair_map(np.asarray(case["reusable"], dtype=bool)[:, None])      # [T, 1, N, N]
+    layer = proAttention(0, ps.get_isp_group())
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    data = drifting_qkv(B, S, H, D, T, seed=case["seed"], drift=case["drift"])
+    outs = []
+    for t in range(T):
+        update_timestep(t)
+        q, k, v = data[t]
+        lo, hi = rank * S // world, (rank + 1) * S // world
+        outs.append(layer.attn(*(x[:, lo:hi].contiguous() for x in (q, k, v))).clone())
+    ret[rank] = (torch.stack(outs), dict(layer.stats))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gpu_pair_worker(rank, world, port, case, ret):
+    """NCCL ranks, real kernels, per-pair reuse map."""
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    import numpy as np
+    from ditango_b200 import ops
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.utils import update_timestep
+    from oracle.ring_oracle import drifting_qkv
+    cfg = init_config(None, make_output_dir=False)
+    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=rank, backend="nccl")
+    c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+    ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+    T = case["T"]
+    cfg.num_layers, cfg.num_inference_steps = 1, T
+    rm = init_redundancy_map(cfg)
+    rm.set_pair_map(np.asarray(case["reusable"], dtype=bool)[:, None])
+    layer = proAttention(0, ps.get_isp_group())
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    data = drifting_qkv(B, S, H, D, T, seed=case["seed"], drift=case["drift"], dtype=torch.bfloat16)
+    lo, hi = rank * S // world, (rank + 1) * S // world
+    outs = []
+    for t in range(T):
+        update_timestep(t)
+        outs.append(layer.attn(*(x[:, lo:hi].contiguous().cuda() for x in data[t])).float().cpu())
+    ret[rank] = (torch.stack(outs), dict(layer.stats), ops.read_status())
+    dist.barrier()
+    dist.destroy_process_group()

@@ -146,3 +146,29 @@ def test_profiling_mode_records_drift_on_device():
         want = O.rel_l1(outs[t], outs[t - 1])
         assert abs(rm.redundancy_map[t, 0].item() - want) <= 1e-5 * max(1.0, want)
     assert not rm.is_auto_setting()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pair_map_attention_multi_gpu(world):
+    """Per-pair Bernoulli(0.6) reuse map (an extension beyond the reference's stride schedule) against the
+    generalised oracle."""
+    if _ngpu() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import numpy as np
+    T = 5
+    rng = np.random.RandomState(3)
+    reusable = rng.rand(T, world, world) < 0.6
+    reusable[0] = False
+    case = dict(T=T, B=2, S=300 * world, H=2, D=64, seed=6, drift=0.05, reusable=reusable.tolist())
+    _PORT[0] += 1
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(W.gpu_pair_worker, args=(world, _PORT[0], case, ret), nprocs=world, join=True)
+    data = O.drifting_qkv(2, 300 * world, 2, 64, T, seed=6, drift=0.05, dtype=torch.bfloat16)
+    want = O.run_pair_map_group(world, reusable, data)
+    for r in range(world):
+        outs, stats, status = ret[r]
+        assert status == 0
+        for t in range(T):
+            e = (outs[t] - want[t][r]).abs()
+            assert e.max() <= 2e-2 and e.mean() <= 1e-3

@@ -98,3 +98,63 @@ def test_dit_output_independent_of_sequence_sharding(mode):
     tol = 2e-2 if mode == "ulysses" else 1e-4
     for r in range(2):
         assert (two[r] - one).abs().max().item() < tol
+
+
+def _bernoulli_pairs(T, world, p, seed):
+    rng = np.random.RandomState(seed)
+    r = rng.rand(T, world, world) < p
+    r[0] = False
+    for i in range(world):
+        r[:, i, i] = False
+    return r
+
+
+@pytest.mark.parametrize("world,p", [(2, 0.5), (4, 0.6)])
+def test_pair_map_attention_matches_generalised_oracle(world, p):
+    """Bernoulli(p) reuse per (step, source chunk, consumer) with step 0 all-fresh -- BASELINE's literal
+    pair maps, which the reference's stride schedule cannot express."""
+    T = 6
+    reusable = _bernoulli_pairs(T, world, p, seed=world)
+    case = dict(T=T, B=1, S=32 * world, H=2, D=16, seed=7, drift=0.05, reusable=reusable.tolist())
+    ret = _spawn(W.pair_worker, world, case)
+    data = O.drifting_qkv(1, 32 * world, 2, 16, T, seed=7, drift=0.05)
+    want = O.run_pair_map_group(world, reusable, data)
+    fetched = 0
+    for r in range(world):
+        for t in range(T):
+            assert (ret[r][0][t] - want[t][r]).abs().max().item() <= 2e-5
+        fetched += ret[r][1]["chunks_received"]
+    assert fetched < T * world * (world - 1)              # some pairs were reused
+
+
+def test_structured_pair_map_far_chunks_reused_after_warmup():
+    """Chunks more than one ring hop away become reusable after step 2 (the shape of BASELINE's
+    Stepvideo map, shrunk): near chunks are always fetched, far ones never again."""
+    world, T = 4, 5
+    reusable = np.zeros((T, world, world), dtype=bool)
+    for t in range(3, T):
+        for src in range(world):
+            for dst in range(world):
+                reusable[t, src, dst] = min((src - dst) % world, (dst - src) % world) > 1
+    case = dict(T=T, B=1, S=128, H=2, D=16, seed=9, drift=0.0, reusable=reusable.tolist())
+    ret = _spawn(W.pair_worker, world, case)
+    data = O.drifting_qkv(1, 128, 2, 16, T, seed=9, drift=0.0)
+    want = O.run_pair_map_group(world, reusable, data)
+    for r in range(world):
+        for t in range(T):
+            assert (ret[r][0][t] - want[t][r]).abs().max().item() <= 2e-5
+        assert ret[r][1]["chunks_received"] == 3 * 3 + 2 * 2    # 3 full steps, then 2 near chunks per step
+    # zero drift: reuse is exact, so every step equals full attention
+    full, _ = O.partial_attention(*data[0])
+    got = torch.cat([ret[r][0][T - 1] for r in range(world)], dim=1)
+    assert (got - full).abs().max().item() < 1e-5
+
+
+def test_tier_b_oracle_reproduces_the_stride_schedule():
+    for world, div in [(4, [1, 4, 4, 2, 2, 2, 1]), (8, [1, 1, 1, 8, 8, 8, 8, 4, 4, 2, 2, 1, 1])]:
+        data = O.drifting_qkv(1, 16 * world, 2, 16, len(div), seed=1)
+        a, _ = O.run_ring_group(world, div, data)
+        b = O.run_pair_map_group(world, O.pair_map_from_dividers(div, world), data)
+        for t in range(len(div)):
+            for r in range(world):
+                assert (a[t][r] - b[t][r]).abs().max().item() <= 2e-6
