@@ -212,8 +212,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    t0 = args.first_step if (args.schedule == "pairs" and args.mode == "ditango") else 0
+
     def one_step(t, qkv, out_sink=None):
-        update_timestep(t % w["steps"])
+        update_timestep((t0 + t) % w["steps"])
         q, k, v = qkv
         last = None
         for l in range(w["layers"]):
@@ -281,7 +283,7 @@ def run_ours(args):
     ev_free = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(t):
-        update_timestep(t % w["steps"])
+        update_timestep((t0 + t) % w["steps"])
         main = torch.cuda.current_stream()
 
         def fetch(l):
@@ -582,6 +584,9 @@ def main():
     ap.add_argument("--workload", default="hunyuan", choices=sorted(WORKLOADS) + ["cogvideox-dit"])
     ap.add_argument("--mode", default="ditango", choices=["ditango", "ring", "ulysses"])
     ap.add_argument("--layers", type=int, default=0, help="override layers per step (debugging only)")
+    ap.add_argument("--first-step", type=int, default=0,
+                    help="--schedule pairs: denoising-step index of the first (warm-up) step; a per-pair cache "
+                         "fills itself from any starting point, the stride schedule must start at step 0")
     ap.add_argument("--schedule", default="stride", choices=["stride", "pairs"],
                     help="ditango mode: stride schedule (what the reference can express) or a per-pair reuse map")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
