@@ -19,7 +19,6 @@ the host cores on a bounded sample of the same workload.
 """
 import argparse
 import json
-import math
 import os
 import statistics
 import subprocess

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 
 from ..logger import init_logger
-from .group_coordinate import GroupCoordinator, SingleRankGroup
+from .group_coordinate import GroupCoordinator
 
 logger = init_logger(__name__)
 

@@ -11,13 +11,12 @@ exchange would address the sending rank itself, and `pair_map()` expands the sch
 boolean reusable[t, src, dst] view of one layer.
 """
 import os
-from typing import List, Optional, Sequence
+from typing import List, Optional
 
 import numpy as np
 import torch
 
 from ..logger import init_logger
-from ..utils import get_timestep
 from .config import get_config
 from .parallel_state import get_usp_group
 

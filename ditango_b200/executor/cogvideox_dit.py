@@ -12,7 +12,7 @@ denoising loop; projections and feed-forward are library GEMMs, the attention is
 """
 import math
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.nn as nn

@@ -5,7 +5,7 @@ extension is missing or an argument is not a CUDA tensor of the expected kind.
 """
 import ctypes
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
