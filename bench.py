@@ -78,7 +78,7 @@ def draw_dividers(steps, layers, world, p, seed=0):
 
 
 def draw_pair_map(workload, steps, layers, world, p, seed=0):
-    """Per-pair reuse map reusable[t, l, src, dst] as BASELINE words it: Bernoulli(p) per (step, layer,
+    """Per-pair reuse map reusable[t, l, src, dst] as the benchmark specification words it: Bernoulli(p) per (step, layer,
     source chunk, consumer) with step 0 all-fresh; for stepvideo the structured map "chunks more than
     two ring hops away are reusable after step 10"."""
     r = np.zeros((steps, layers, world, world), dtype=bool)
@@ -436,7 +436,7 @@ def run_reference(args):
 
 
 def run_dit(args):
-    """BASELINE config 5: random-init CogVideoX-5B-shaped DiT (42 layers, hidden 3072, 48 x 64 heads),
+    """Benchmark configuration 5: random-init CogVideoX-5B-shaped DiT (42 layers, hidden 3072, 48 x 64 heads),
     latent 13x60x90x16 + 226 text tokens, classifier-free guidance in-batch (B = 2), bf16; one step =
     one denoising step of the whole model.  Prints ms per step and exposed communication."""
     import torch.distributed as dist

@@ -136,7 +136,7 @@ def _worker(rank, world, case, refpkg, port, ret):
 
 
 CASES = {
-    # BASELINE config 1: two ranks, B1 H4 S1024 D64 fp32, 4 steps, Bernoulli(0.5) reuse with
+    # Benchmark configuration 1 (the CPU-runnable case): two ranks, B1 H4 S1024 D64 fp32, 4 steps, Bernoulli(0.5) reuse with
     # step 0 full -> dividers 1,2,2,1 is one draw of it that exercises both transitions.
     "cfg1_n2": dict(world=2, B=1, S=1024, H=4, D=64, seed=0, drift=0.05, dividers=[1, 2, 2, 1], row_step=16),
     # The seven-step schedule whose state-machine trace is known (strides 4,1,1,2,2,2,4).

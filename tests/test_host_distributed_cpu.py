@@ -111,7 +111,7 @@ def _bernoulli_pairs(T, world, p, seed):
 
 @pytest.mark.parametrize("world,p", [(2, 0.5), (4, 0.6)])
 def test_pair_map_attention_matches_generalised_oracle(world, p):
-    """Bernoulli(p) reuse per (step, source chunk, consumer) with step 0 all-fresh -- BASELINE's literal
+    """Bernoulli(p) reuse per (step, source chunk, consumer) with step 0 all-fresh -- the benchmark specification's literal
     pair maps, which the reference's stride schedule cannot express."""
     T = 6
     reusable = _bernoulli_pairs(T, world, p, seed=world)
@@ -128,7 +128,7 @@ def test_pair_map_attention_matches_generalised_oracle(world, p):
 
 
 def test_structured_pair_map_far_chunks_reused_after_warmup():
-    """Chunks more than one ring hop away become reusable after step 2 (the shape of BASELINE's
+    """Chunks more than one ring hop away become reusable after step 2 (the shape of the benchmark specification's
     Stepvideo map, shrunk): near chunks are always fetched, far ones never again."""
     world, T = 4, 5
     reusable = np.zeros((T, world, world), dtype=bool)

@@ -1,6 +1,6 @@
 """GPU parity of the three kernels, called through the C ABI, against the CPU oracle.
 
-Tolerances (BASELINE north star): bf16 outputs <= 2e-2 max-abs and <= 1e-3 mean-abs; fp32 lse
+Tolerances (the stated parity targets): bf16 outputs <= 2e-2 max-abs and <= 1e-3 mean-abs; fp32 lse
 <= 1e-3.  fp32 outputs computed from bf16 inputs meet the same bounds with margin."""
 import math
 
