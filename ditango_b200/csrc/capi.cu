@@ -99,12 +99,13 @@ int load_encoder() {
   return DTB_OK;
 }
 
-// 2-D bf16 view [rows, width] with a row pitch of tok_stride elements; boxes of 64 x 128 elements
-// (128 bytes x 128 rows) written to shared memory with the 128-byte swizzle.
-int make_tile_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t width, int64_t tok_stride, const char* what) {
+// 2-D bf16 view [rows, width] with a row pitch of tok_stride elements; boxes of 64 x box_rows elements
+// (128 bytes x box_rows rows) written to shared memory with the 128-byte swizzle.
+int make_tile_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t width, int64_t tok_stride, int box_rows,
+                  const char* what) {
   cuuint64_t gdim[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
   cuuint64_t gstride[1] = {static_cast<cuuint64_t>(tok_stride) * 2};
-  cuuint32_t box[2] = {64, 128};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -185,9 +186,10 @@ DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
   CUtensorMap tq, tk, tv;
   // A tensor map needs at least one row; an empty key chunk never issues a load.
   const int64_t rows_k = total_k > 0 ? total_k : 1;
-  if ((rc = make_tile_map(&tq, q, total_q, width, q_tok_stride, "q")) != DTB_OK) return rc;
-  if ((rc = make_tile_map(&tk, k, rows_k, width, k_tok_stride, "k")) != DTB_OK) return rc;
-  if ((rc = make_tile_map(&tv, v, rows_k, width, v_tok_stride, "v")) != DTB_OK) return rc;
+  const int kv_rows = dtb::flash_kv_box_rows(head_dim);
+  if ((rc = make_tile_map(&tq, q, total_q, width, q_tok_stride, 128, "q")) != DTB_OK) return rc;
+  if ((rc = make_tile_map(&tk, k, rows_k, width, k_tok_stride, kv_rows, "k")) != DTB_OK) return rc;
+  if ((rc = make_tile_map(&tv, v, rows_k, width, v_tok_stride, kv_rows, "v")) != DTB_OK) return rc;
 
   dtb::FlashParams p;
   p.out = out;

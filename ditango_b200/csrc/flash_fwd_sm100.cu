@@ -8,16 +8,24 @@
 //   warp  8     TMA producer: Q tiles once, then K_j, V_j tiles through a shared-memory ring
 //   warp  9     MMA issuer (one elected thread): S_i = Q_i K_j^T and O_i += P_i V_j via tcgen05.mma
 // Tensor memory (512 columns x 128 lanes of fp32): S_0 [0,128), S_1 [128,256), O_0 [256,256+D),
-// O_1 [256+D,256+2D).
-//   D = 128: the map is full, so P_i (bf16) overwrites the first 64 columns of S_i.  Issue order
-//       S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
-//     the softmax of one Q tile runs while the pipe works on the other tile.
-//   D = 64: 128 columns are left, so P_i gets its own columns [384 + 64 i, 448 + 64 i).  S_i(j+1) is
-//     then issued as soon as the softmax group has pulled S_i(j) into registers, ahead of PV_i(j):
+// O_1 [256+D,256+2D).  Three schedules, chosen at compile time by what fits:
+//   D = 64 ("decoupled"): 128 columns are left, so P_i (bf16) gets its own columns [384 + 64 i,
+//     448 + 64 i).  Key tiles of 128 rows; S_i(j+1) is issued as soon as the softmax group has pulled
+//     S_i(j) into registers, ahead of PV_i(j):
 //       S0(0) S1(0) | S0(j+1) S1(j+1) PV0(j) PV1(j) | ...
-//     and in steady state a softmax group never waits for the tensor pipe.
-// P is handed to the MMA issuer in two halves (keys 0-63, 64-127) so the first PV steps start while
-// the second half is still being exponentiated.
+//     and in steady state a softmax group never waits for the tensor pipe.  P is handed to the MMA
+//     issuer in two halves (keys 0-63, 64-127) so the first PV steps start while the second half is
+//     still being exponentiated.
+//   D = 128 ("split", DTB_SPLIT_KV=1, the default): the map is full.  Key tiles of 64 rows and two S
+//     buffers of 64 columns per Q tile: S_i(j) sits in buffer j & 1 and P_i(j) overwrites its first 32
+//     columns.  S_i(j+2) follows PV_i(j) on the pipe, so S_i(j+1) is already there when a softmax
+//     group finishes tile j:
+//       S0(0) S1(0) S0(1) S1(1) | PV0(j) S0(j+2) PV1(j) S1(j+2) | ...
+//     The price: Q is re-read from shared memory per 64 keys instead of per 128, and an N=64 MMA does
+//     not run at the rate of an N=128 one.
+//   D = 128 ("coupled", DTB_SPLIT_KV=0): key tiles of 128 rows, P_i over the first 64 columns of S_i,
+//       S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
+//     each Q tile runs the serial chain softmax -> PV -> next S; only the other tile's work overlaps.
 // Running max is kept lazily: O is rescaled only when the max grew by more than 2^8, which bounds
 // every probability by 2^8 and keeps bf16 P exact enough; the final normalisation undoes it.
 #include "flash_fwd_sm100.cuh"
@@ -29,34 +37,45 @@ namespace dtb {
 
 namespace {
 
+#ifndef DTB_SPLIT_KV
+#define DTB_SPLIT_KV 1
+#endif
+#ifndef DTB_SPLIT_TURNS
+#define DTB_SPLIT_TURNS 1
+#endif
+
 constexpr int kBM = 128;        // query rows per tile
-constexpr int kBN = 128;        // key rows per tile
 constexpr int kQT = 2;          // query tiles per CTA
 constexpr int kThreads = 320;
 constexpr int kTmaWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kSlabBytes = 128 * 128;   // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
+constexpr int kSlabBytes = 128 * 128;   // one TMA box of Q: 128 rows x 64 bf16, 128-byte swizzled
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 template <int D>
 struct Cfg {
   static constexpr int kSlabs = D / 64;
-  static constexpr int kTileBytes = 128 * D * 2;
-  static constexpr int kStages = (D == 128) ? 4 : 6;
+  // 64-key tiles with double-buffered S (see the head of this file)
+  static constexpr bool kSplit = (D == 128) && (DTB_SPLIT_KV != 0);
+  static constexpr int kBN = kSplit ? 64 : 128;          // key rows per tile
+  static constexpr int kTileBytes = 128 * D * 2;         // one Q tile
+  static constexpr int kKvTileBytes = kBN * D * 2;       // one K or V tile
+  static constexpr int kKvSlabBytes = kBN * 128;         // one TMA box of K / V: kBN rows x 64 bf16
+  static constexpr int kStages = kSplit ? 8 : ((D == 128) ? 4 : 6);
   // P in its own tensor-memory columns and S_i(j+1) issued ahead of PV_i(j)
-  static constexpr bool kDecoupled = (256 + 2 * D + 128 <= 512);
+  static constexpr bool kDecoupled = !kSplit && (256 + 2 * D + 128 <= 512);
   // sibling warps of the two softmax groups alternate in the exp phase
-  static constexpr bool kTurns = kDecoupled;
+  static constexpr bool kTurns = kDecoupled || (kSplit && DTB_SPLIT_TURNS != 0);
   // of every 4 score pairs, this many take the polynomial exp2 instead of the ex2 unit
 #ifdef DTB_EMU_PAIRS
   static constexpr int kEmuPairs = DTB_EMU_PAIRS;
 #else
   static constexpr int kEmuPairs = 0;
 #endif
-  // barriers: q_full, kv_full[S], kv_empty[S], s_full[2], p_full[4], s_free[2], pv_done[2], exp_turn[8], o_final
-  static constexpr int kBars = 1 + 2 * kStages + 2 + 4 + 2 + 2 + 8 + 1;
-  static constexpr int kSmemBytes = 1024 + (kQT + kStages) * kTileBytes + kBars * 8 + 16;
+  // barriers: q_full, kv_full[S], kv_empty[S], s_full[4], p_full[4], s_free[2], pv_done[2], exp_turn[8], o_final
+  static constexpr int kBars = 1 + 2 * kStages + 4 + 4 + 2 + 2 + 8 + 1;
+  static constexpr int kSmemBytes = 1024 + kQT * kTileBytes + kStages * kKvTileBytes + kBars * 8 + 16;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS = 0;                                  // + tile * 128
   static constexpr uint32_t kColO = 256;                                // + tile * D
@@ -127,16 +146,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const FlashParams p) {
   using C = Cfg<D>;
+  constexpr int kBN = C::kBN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_q = smem;
   uint8_t* s_kv = smem + kQT * C::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + C::kStages * C::kTileBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_kv + C::kStages * C::kKvTileBytes);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + C::kStages;
-  uint64_t* s_full = kv_empty + C::kStages;   // [tile]: S_tile(j) is in tensor memory
-  uint64_t* p_full = s_full + 2;              // [tile*2 + half]: P of keys [64 half, 64 half + 64) written
+  uint64_t* s_full = kv_empty + C::kStages;   // [tile] (split: [tile*2 + buffer]): S_tile(j) is in tensor memory
+  uint64_t* p_full = s_full + 4;              // [tile*2 + half]: P of keys [64 half, 64 half + 64) written
+                                              // (split: [tile*2 + buffer], the whole 64-key tile)
   uint64_t* s_free = p_full + 4;              // [tile]: S_tile(j) has been read into registers (decoupled)
   uint64_t* pv_done = s_free + 2;             // [tile]: PV_tile(j) has completed (decoupled)
   uint64_t* exp_turn = pv_done + 2;           // [tile*4 + quarter]: the sibling warp finished its exp phase
@@ -186,8 +207,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   // Position of K_j / V_j in the order the ring carries them.
   //   coupled:   K_0 V_0 K_1 V_1 ...                 (K_j at 2j, V_j at 2j+1)
   //   decoupled: K_0 K_1 V_0 K_2 V_1 ... V_{n-1}     (K_{j+1} is consumed before V_j)
-  auto k_slot = [&](int j) { return C::kDecoupled ? (j == 0 ? 0 : 2 * j - 1) : 2 * j; };
-  auto v_slot = [&](int j) { return C::kDecoupled ? (j < n_tiles - 1 ? 2 * j + 2 : 2 * j + 1) : 2 * j + 1; };
+  //   split:     K_0 K_1 V_0 K_2 V_1 ... K_{n-1} V_{n-2} V_{n-1}   (K_{j+2} follows V_j)
+  auto k_slot = [&](int j) {
+    if (C::kSplit) return j < 2 ? j : 2 * j - 1;
+    return C::kDecoupled ? (j == 0 ? 0 : 2 * j - 1) : 2 * j;
+  };
+  auto v_slot = [&](int j) {
+    if (C::kSplit) return j < n_tiles - 1 ? 2 * j + 2 : 2 * j + 1;
+    return C::kDecoupled ? (j < n_tiles - 1 ? 2 * j + 2 : 2 * j + 1) : 2 * j + 1;
+  };
 
   // ------------------------------------------------------------------ set-up
   if (threadIdx.x == kTmaWarp * 32) {
@@ -196,8 +224,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
       mbar_init(&s_free[i], kBM);
       mbar_init(&pv_done[i], 1);
     }
@@ -233,7 +261,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int it = 0; it < n_loads; ++it) {
         bool is_v;
         int j;
-        if (C::kDecoupled) {
+        if (C::kSplit) {
+          if (it == n_loads - 1) { is_v = true; j = n_tiles - 1; }
+          else if (it < 2) { is_v = false; j = it; }
+          else if (it & 1) { is_v = false; j = (it + 1) >> 1; }
+          else { is_v = true; j = (it - 2) >> 1; }
+        } else if (C::kDecoupled) {
           if (it == 0) { is_v = false; j = 0; }
           else if (it == n_loads - 1) { is_v = true; j = n_tiles - 1; }
           else if (it & 1) { is_v = false; j = (it + 1) >> 1; }
@@ -245,11 +278,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int stage = it % C::kStages;
         const int round = it / C::kStages;
         if (round > 0 && !wait_or_abort(&kv_empty[stage], (round - 1) & 1, p.status, 11)) break;
-        mbar_expect_tx(&kv_full[stage], C::kTileBytes);
+        mbar_expect_tx(&kv_full[stage], C::kKvTileBytes);
         const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
         const int row = k_begin + j * kBN;
         for (int s = 0; s < C::kSlabs; ++s)
-          tma_load_2d(s_kv + stage * C::kTileBytes + s * kSlabBytes, tm, &kv_full[stage], head * D + s * 64, row);
+          tma_load_2d(s_kv + stage * C::kKvTileBytes + s * C::kKvSlabBytes, tm, &kv_full[stage], head * D + s * 64, row);
       }
     }
     __syncwarp();
@@ -261,23 +294,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t q_addr = smem_u32(s_q);
       const uint32_t kv_addr = smem_u32(s_kv);
 
-      auto issue_s = [&](int tile, int stage) {
+      // S_tile = Q_tile K^T into S columns [128 tile + s_col, ... + kBN)
+      auto issue_s = [&](int tile, int stage, int s_col = 0) {
 #pragma unroll
         for (int k16 = 0; k16 < D / 16; ++k16) {
-          const uint32_t off = (k16 >> 2) * kSlabBytes + (k16 & 3) * 32;
-          const uint64_t a = smem_desc_sw128(q_addr + tile * C::kTileBytes + off, 16, 1024);
-          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kTileBytes + off, 16, 1024);
-          mma_ss(tmem_base + C::kColS + tile * kBN, a, b, idesc_qk, k16 > 0);
+          const uint32_t in_slab = (k16 & 3) * 32;
+          const uint64_t a = smem_desc_sw128(q_addr + tile * C::kTileBytes + (k16 >> 2) * kSlabBytes + in_slab, 16, 1024);
+          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kKvTileBytes + (k16 >> 2) * C::kKvSlabBytes + in_slab, 16, 1024);
+          mma_ss(tmem_base + C::kColS + tile * 128 + s_col, a, b, idesc_qk, k16 > 0);
         }
       };
-      // half h covers keys [64 h, 64 h + 64) of the tile: four K=16 steps
-      auto issue_pv = [&](int tile, int stage, int half, bool acc) {
+      // half h covers keys [64 h, 64 h + 64) of the tile: four K=16 steps of P (at column p_col) times V
+      auto issue_pv = [&](int tile, int stage, int half, bool acc, uint32_t p_col) {
 #pragma unroll
-        for (int kk = 0; kk < kBN / 32; ++kk) {
-          const int k16 = half * (kBN / 32) + kk;
-          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kTileBytes + k16 * 2048, kSlabBytes, 1024);
-          mma_ts(tmem_base + C::kColO + tile * D, tmem_base + C::kColP + tile * C::kStrideP + k16 * 8, b, idesc_pv,
-                 (acc || k16 > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {
+          const int k16 = half * 4 + kk;
+          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kKvTileBytes + k16 * 2048, C::kKvSlabBytes, 1024);
+          mma_ts(tmem_base + C::kColO + tile * D, tmem_base + p_col + k16 * 8, b, idesc_pv, (acc || k16 > 0) ? 1u : 0u);
         }
       };
       auto stage_of = [&](int it) { return it % C::kStages; };
@@ -290,14 +323,57 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!wait_or_abort(&p_full[tile * 2], j & 1, p.status, 24 + tile)) return false;
         DTB_STAMP(2, j, 3 + 2 * tile);
         tc_fence_after();
-        issue_pv(tile, stage, 0, j > 0);
+        issue_pv(tile, stage, 0, j > 0, C::kColP + tile * C::kStrideP);
         if (!wait_or_abort(&p_full[tile * 2 + 1], j & 1, p.status, 26 + tile)) return false;
         tc_fence_after();
-        issue_pv(tile, stage, 1, true);
+        issue_pv(tile, stage, 1, true, C::kColP + tile * C::kStrideP);
         return true;
       };
 
       bool ok = wait_or_abort(q_full, 0, p.status, 21);
+      if constexpr (C::kSplit) {
+        // S(0) and S(1) of both Q tiles fill the two buffers; from then on S(j+2) follows PV(j).
+        for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+          ok = wait_kv(k_slot(j), 22);
+          if (!ok) break;
+          tc_fence_after();
+          for (int tile = 0; tile < 2; ++tile) {
+            issue_s(tile, stage_of(k_slot(j)), j * kBN);
+            mma_commit(&s_full[tile * 2 + j]);
+          }
+          mma_commit(&kv_empty[stage_of(k_slot(j))]);
+        }
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          const int buf = j & 1;
+          const bool more = (j + 2 < n_tiles);
+          const int it_v = v_slot(j), it_kn = k_slot(j + 2);
+          DTB_STAMP(2, j, 0);
+          ok = wait_kv(it_v, 23);
+          if (!ok) break;
+          DTB_STAMP(2, j, 1);
+          for (int tile = 0; tile < 2; ++tile) {
+            ok = wait_or_abort(&p_full[tile * 2 + buf], (j >> 1) & 1, p.status, 24 + tile);
+            if (!ok) break;
+            DTB_STAMP(2, j, 2 + 2 * tile);
+            tc_fence_after();
+            issue_pv(tile, stage_of(it_v), 0, j > 0, C::kColS + tile * 128 + buf * kBN);
+            mma_commit(&pv_done[tile]);
+            if (tile == 1) mma_commit(&kv_empty[stage_of(it_v)]);
+            if (more) {
+              if (tile == 0) {
+                ok = wait_kv(it_kn, 25);
+                if (!ok) break;
+                tc_fence_after();
+              }
+              // overwrites P_tile(j); the pipe runs it behind PV_tile(j)
+              issue_s(tile, stage_of(it_kn), buf * kBN);
+              mma_commit(&s_full[tile * 2 + buf]);
+              if (tile == 1) mma_commit(&kv_empty[stage_of(it_kn)]);
+            }
+            DTB_STAMP(2, j, 3 + 2 * tile);
+          }
+        }
+      } else {
       if (ok) ok = wait_kv(k_slot(0), 22);
       if (ok) {
         tc_fence_after();
@@ -360,6 +436,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           DTB_STAMP(2, j, 3);
         }
       }
+      }
       if (ok) mma_commit(o_final);
     }
     __syncwarp();
@@ -368,7 +445,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int tile = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t s_taddr = lane_base + C::kColS + tile * kBN;
+    const uint32_t s_taddr = lane_base + C::kColS + tile * 128;
     const uint32_t p_taddr = lane_base + C::kColP + tile * C::kStrideP;
     const uint32_t o_taddr = lane_base + C::kColO + tile * D;
     const float c = p.scale_log2;
@@ -378,6 +455,101 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const bool stamp = (lane == 0 && (warp & 3) == 0);
     (void)stamp;
 
+    if constexpr (C::kSplit) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int buf = j & 1;
+        const uint32_t sb_taddr = s_taddr + buf * kBN;   // S_tile(j), then P_tile(j) over its first half
+        if (stamp) DTB_STAMP(tile, j, 0);
+        ok = wait_or_abort(&s_full[tile * 2 + buf], (j >> 1) & 1, p.status, 31 + tile);
+        if (!ok) break;
+        if (stamp) DTB_STAMP(tile, j, 1);
+        tc_fence_after();
+        uint32_t sr[kBN];
+        tmem_ld32(sb_taddr, sr);
+        tmem_ld32(sb_taddr + 32, sr + 32);
+        tmem_wait_ld();
+        if ((j == n_tiles - 1) && (k_len & (kBN - 1)) != 0) {
+          const int valid = k_len - j * kBN;
+#pragma unroll
+          for (int i = 0; i < kBN; ++i)
+            if (i >= valid) sr[i] = 0xff800000u;   // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kBN; i += 8) {
+          mx0 = max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+          mx2 = max3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+          mx3 = max3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+        }
+        if (stamp) DTB_STAMP(tile, j, 2);
+        const float m_new = fmaxf(max3(m, mx0, mx1), fmaxf(mx2, mx3));
+        if (j == 0) {
+          m = m_new;
+        } else {
+          const bool grow = (m_new - m) * c > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            // O is rescaled in place: PV_tile(j-1) must have drained (PV_tile(j) is not issued before
+            // this group hands over P_tile(j), so nothing else is in flight on O)
+            ok = wait_or_abort(&pv_done[tile], (j - 1) & 1, p.status, 33 + tile);
+            if (!ok) break;
+            tc_fence_after();
+            const float f = ex2((m - m_new) * c);
+#pragma unroll
+            for (int q = 0; q < D / 32; ++q) {
+              uint32_t orow[32];
+              tmem_ld32(o_taddr + q * 32, orow);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+              tmem_st32(o_taddr + q * 32, orow);
+            }
+            tmem_wait_st();
+            l *= f;
+            m = m_new;
+          }
+        }
+        if (stamp) DTB_STAMP(tile, j, 3);
+        if (C::kTurns) {
+          ok = wait_or_abort(&exp_turn[tile * 4 + (warp & 3)], tile == 0 ? ((j & 1) ^ 1) : (j & 1), p.status, 35 + tile);
+          if (!ok) break;
+        }
+        const float nmc = -m * c;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        uint32_t pk[kBN / 2];
+#pragma unroll
+        for (int g = 0; g < kBN / 8; ++g) {
+#pragma unroll
+          for (int pr = 0; pr < 4; ++pr) {
+            const int i = g * 8 + pr * 2;
+            const float x0 = fmaf(__uint_as_float(sr[i]), c, nmc);
+            const float x1 = fmaf(__uint_as_float(sr[i + 1]), c, nmc);
+            float p0, p1;
+            if (pr >= 4 - C::kEmuPairs) {
+              exp2_poly_pair(x0, x1, p0, p1);
+            } else {
+              p0 = ex2(x0);
+              p1 = ex2(x1);
+            }
+            if (pr & 1) {
+              sum2 += p0;
+              sum3 += p1;
+            } else {
+              sum0 += p0;
+              sum1 += p1;
+            }
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          }
+        }
+        tmem_st32(sb_taddr, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[tile * 2 + buf]);
+        if (stamp) DTB_STAMP(tile, j, 4);
+        if (C::kTurns) mbar_arrive(&exp_turn[(tile ^ 1) * 4 + (warp & 3)]);
+        l += (sum0 + sum1) + (sum2 + sum3);
+      }
+    } else {
     for (int j = 0; j < n_tiles; ++j) {
       if (stamp) DTB_STAMP(tile, j, 0);
       ok = wait_or_abort(&s_full[tile], j & 1, p.status, 31 + tile);
@@ -502,6 +674,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (C::kTurns) mbar_arrive(&exp_turn[(tile ^ 1) * 4 + (warp & 3)]);
       l += (sum0 + sum1) + (sum2 + sum3);
     }
+    }
 
     if (ok) ok = wait_or_abort(o_final, 0, p.status, 41);
     if (ok) {
@@ -598,6 +771,8 @@ cudaError_t launch_flash(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   flash_fwd_kernel<D><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
   return cudaGetLastError();
 }
+
+int flash_kv_box_rows(int head_dim) { return head_dim == 128 ? Cfg<128>::kBN : Cfg<64>::kBN; }
 
 #ifdef DTB_FLASH_TIMING
 cudaError_t read_flash_timing(long long* host, int n) {

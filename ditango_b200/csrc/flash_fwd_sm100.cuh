@@ -28,4 +28,8 @@ template <int D>
 cudaError_t launch_flash(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                          const FlashParams& p, cudaStream_t stream);
 
+// Rows of one K / V tile: the tensor maps of k and v must be encoded with boxes of 64 x this many elements
+// (q always uses 64 x 128).
+int flash_kv_box_rows(int head_dim);
+
 }  // namespace dtb
