@@ -44,6 +44,7 @@ namespace {
 #define DTB_SPLIT_TURNS 1
 #endif
 
+
 constexpr int kBM = 128;        // query rows per tile
 constexpr int kQT = 2;          // query tiles per CTA
 constexpr int kThreads = 320;
@@ -294,24 +295,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t q_addr = smem_u32(s_q);
       const uint32_t kv_addr = smem_u32(s_kv);
 
+      // Descriptors are built once; a tile, stage or K step only moves the start-address field (units
+      // of 16 bytes, no carry out of the field: shared memory ends below 2^18).
+      const uint64_t q_desc = smem_desc_sw128(q_addr, 16, 1024);                  // K-major
+      const uint64_t k_desc = smem_desc_sw128(kv_addr, 16, 1024);                 // K-major
+      const uint64_t v_desc = smem_desc_sw128(kv_addr, C::kKvSlabBytes, 1024);    // MN-major, slab pitch leading
       // S_tile = Q_tile K^T into S columns [128 tile + s_col, ... + kBN)
       auto issue_s = [&](int tile, int stage, int s_col = 0) {
+        const uint64_t a0 = q_desc + static_cast<uint32_t>(tile * (C::kTileBytes >> 4));
+        const uint64_t b0 = k_desc + static_cast<uint32_t>(stage * (C::kKvTileBytes >> 4));
+        const uint32_t d = tmem_base + C::kColS + tile * 128 + s_col;
 #pragma unroll
         for (int k16 = 0; k16 < D / 16; ++k16) {
           const uint32_t in_slab = (k16 & 3) * 32;
-          const uint64_t a = smem_desc_sw128(q_addr + tile * C::kTileBytes + (k16 >> 2) * kSlabBytes + in_slab, 16, 1024);
-          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kKvTileBytes + (k16 >> 2) * C::kKvSlabBytes + in_slab, 16, 1024);
-          mma_ss(tmem_base + C::kColS + tile * 128 + s_col, a, b, idesc_qk, k16 > 0);
+          mma_ss(d, a0 + (((k16 >> 2) * kSlabBytes + in_slab) >> 4), b0 + (((k16 >> 2) * C::kKvSlabBytes + in_slab) >> 4),
+                 idesc_qk, k16 > 0);
         }
       };
       // half h covers keys [64 h, 64 h + 64) of the tile: four K=16 steps of P (at column p_col) times V
       auto issue_pv = [&](int tile, int stage, int half, bool acc, uint32_t p_col) {
+        const uint64_t b0 = v_desc + static_cast<uint32_t>(stage * (C::kKvTileBytes >> 4) + half * (4 * 2048 >> 4));
+        const uint32_t d = tmem_base + C::kColO + tile * D;
+        const uint32_t a = tmem_base + p_col + half * 32;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const int k16 = half * 4 + kk;
-          const uint64_t b = smem_desc_sw128(kv_addr + stage * C::kKvTileBytes + k16 * 2048, C::kKvSlabBytes, 1024);
-          mma_ts(tmem_base + C::kColO + tile * D, tmem_base + p_col + k16 * 8, b, idesc_pv, (acc || k16 > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(d, a + kk * 8, b0 + (kk * 2048 >> 4), idesc_pv, (acc || kk > 0 || half > 0) ? 1u : 0u);
       };
       auto stage_of = [&](int it) { return it % C::kStages; };
       auto parity_of = [&](int it) { return static_cast<uint32_t>((it / C::kStages) & 1); };
@@ -514,6 +522,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = wait_or_abort(&exp_turn[tile * 4 + (warp & 3)], tile == 0 ? ((j & 1) ^ 1) : (j & 1), p.status, 35 + tile);
           if (!ok) break;
         }
+        if (stamp) DTB_STAMP(tile, j, 4);
         const float nmc = -m * c;
         float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
         uint32_t pk[kBN / 2];
@@ -541,11 +550,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             pk[i >> 1] = pack_bf16x2(p0, p1);
           }
         }
+        if (stamp) DTB_STAMP(tile, j, 5);
         tmem_st32(sb_taddr, pk);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&p_full[tile * 2 + buf]);
-        if (stamp) DTB_STAMP(tile, j, 4);
+        if (stamp) DTB_STAMP(tile, j, 6);
+        // Handing the turn over any earlier (after the exp loop, or part-way through it) was measured
+        // 10 % slower: the two groups then drift into phase and exponentiate side by side.
         if (C::kTurns) mbar_arrive(&exp_turn[(tile ^ 1) * 4 + (warp & 3)]);
         l += (sum0 + sum1) + (sum2 + sum3);
       }
