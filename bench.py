@@ -56,10 +56,10 @@ def measured_peaks():
 
 def flash_dram_traffic(B, S_q, H, D):
     """DRAM bytes of one flash launch on a square chunk pair, scaled from the ncu captures under
-    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): 429.7 MB at B1 S14882 H24 D128 and
+    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): 424.6 MB at B1 S14882 H24 D128 and
     519.0 MB at B2 S8888 H48 D64.  K and V of a head stay in L2 while its query tiles run, so traffic
     follows the tensor sizes (tokens x heads x head_dim), not the FLOPs."""
-    ref = {128: (429.7e6, 1 * 14882 * 24 * 128), 64: (519.0e6, 2 * 8888 * 48 * 64)}[D]
+    ref = {128: (424.6e6, 1 * 14882 * 24 * 128), 64: (519.0e6, 2 * 8888 * 48 * 64)}[D]
     return ref[0] * (B * S_q * H * D) / ref[1]
 
 
