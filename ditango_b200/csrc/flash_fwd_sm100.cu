@@ -85,7 +85,12 @@ struct Cfg {
 };
 
 #ifdef DTB_FLASH_TIMING
-// Development aid: per-phase SM clock stamps of one CTA (roles: softmax group 0, 1, MMA issuer).
+// Development aid: per-phase SM clock stamps of one CTA, g_flash_timing[role][key tile j < 48][phase],
+// read back with dtb_debug_flash_timing (exported only in this build).  Roles 0, 1: first warp of each
+// softmax group; role 2: the MMA issuer.  Phases of the split schedule --
+//   softmax: 0 before the wait for S, 1 S ready, 2 row max known, 3 rescale decided, 4 exp turn acquired,
+//            5 exp loop done, 6 P handed over;
+//   issuer:  0 top of step, 1 V ready, 2 P0 ready, 3 PV0 + S0(j+2) issued, 4 P1 ready, 5 PV1 + S1(j+2) issued.
 __device__ long long g_flash_timing[3 * 48 * 8];
 #define DTB_STAMP(role, j, phase)                                                                      \
   do {                                                                                                 \
