@@ -201,6 +201,7 @@ def run_ours(args):
         rm.divider_map = torch.from_numpy(draw_dividers(w["steps"], w["layers"], world, w["p"]))
         rm._refine_divider_map()
         rm.screen_self_sends()
+    proAttention.hop_grouping = args.hop_grouping
     layers = [proAttention(l, group) for l in range(w["layers"])]
     raw, gen = make_inputs(w, rank, world, device)
     B, H, D, S = w["B"], w["H"], w["D"], w["S"]
@@ -351,7 +352,8 @@ def run_ours(args):
                        "mode": args.mode, "global_batch": B, "seq_len": S, "layers_per_step": w["layers"],
                        "l2": "inputs larger than L2 (Q,K,V of one layer call exceed 126 MB)",
                        "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0,
-                       "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none"},
+                       "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none",
+                       "hop_grouping": args.hop_grouping if (args.mode != "ulysses" and world > 1) else "none"},
             "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
             "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
             "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
@@ -442,6 +444,7 @@ def run_dit(args):
     import torch.distributed as dist
     from ditango_b200 import _capi, ops
     from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.attention import proAttention
     from ditango_b200.core.config import init_config
     from ditango_b200.core.group_coordinate import SingleRankGroup
     from ditango_b200.core.redundancy_map import init_redundancy_map
@@ -473,6 +476,7 @@ def run_dit(args):
         rm._refine_divider_map()
         rm.screen_self_sends()
     torch.manual_seed(0)
+    proAttention.hop_grouping = args.hop_grouping
     with torch.device(device):
         model = CogVideoXDiT(dcfg, group, mode=args.mode).to(torch.bfloat16)
     g = torch.Generator(device=device).manual_seed(0)
@@ -588,6 +592,8 @@ def main():
                          "fills itself from any starting point, the stride schedule must start at step 0")
     ap.add_argument("--schedule", default="stride", choices=["stride", "pairs"],
                     help="ditango mode: stride schedule (what the reference can express) or a per-pair reuse map")
+    ap.add_argument("--hop-grouping", default="single", choices=["single", "doubling"],
+                    help="transport batches per call: one per hop, or batches of 1, 2, 4, ... hops")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy"], help="time one kernel and exit")

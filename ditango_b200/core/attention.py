@@ -53,6 +53,10 @@ def release_receive_slots():
 
 
 class proAttention:
+    # How the hops of one call are batched for the transport ("single" or "doubling", see _post_hops).
+    # Class-wide default; every rank of a group must agree.
+    hop_grouping = "single"
+
     def __init__(self, layer_id: int, isp_group):
         self.group = isp_group
         self.isp_size = self.group.world_size
@@ -78,9 +82,9 @@ class proAttention:
         self._comm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
 
     # ------------------------------------------------------------------ transport
-    def _post_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
-        """Post this rank's sends of its own chunk and its receive for `hop` as one batch of its own.
-        Returns (received tensors or None, batch handle)."""
+    def _queue_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
+        """Queue this rank's sends of its own chunk and its receive for `hop`; returns the received
+        tensors (None when nothing arrives in this hop)."""
         me = self.local_chunk_id
         src = plan.recv_from(me, hop)
         recv = None
@@ -91,9 +95,30 @@ class proAttention:
             recv = tuple(self.group.p2p_irecv(src=src, out=_slot(f"kv{i}", hop, t)) for i, t in enumerate(payload))
             self.stats["chunks_received"] += 1
             self.stats["bytes_received"] += sum(t.numel() * t.element_size() for t in payload)
-        return recv, self.group.p2p_commit_batch()
+        return recv
+
+    def _post_hops(self, plan: StepPlan, n_hops: int, payload: Tuple[torch.Tensor, ...]):
+        """Post every hop of this call.  Returns one (received tensors or None, batch handle or None)
+        per hop; the handle sits on the first hop of its batch and covers the hops up to the next handle.
+
+        hop_grouping "single": one batch per hop -- a batch is one NCCL group, and the groups of a
+        process group run one after another, each moving one chunk per rank at the rate of one peer pair.
+        "doubling": batches of 1, 2, 4, ... hops -- the first chunk still arrives as early as possible,
+        later batches pull from several peers at once.  Every rank of the group must use the same setting."""
+        posted, size, hop = [], 1, 0
+        while hop < n_hops:
+            end = min(n_hops, hop + size)
+            recvs = [self._queue_hop(plan, h, payload) for h in range(hop, end)]
+            handle = self.group.p2p_commit_batch()
+            posted.extend((r, handle if i == 0 else None) for i, r in enumerate(recvs))
+            hop = end
+            if self.hop_grouping == "doubling":
+                size *= 2
+        return posted
 
     def _wait_hop(self, handle):
+        if handle is None:          # covered by the batch of an earlier hop
+            return
         if self.measure_comm and torch.cuda.is_available():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -129,7 +154,7 @@ class proAttention:
             return _engine.flash_partial(query, kv[0], kv[1], lse_layout=LSE_BHS, **kw)
 
         plan = plan_pair_step(N, flags, self._have)
-        posted = [self._post_hop(plan, hop, payload) for hop in range(plan.n_hops)]
+        posted = self._post_hops(plan, plan.n_hops, payload)
         own = attend(payload)
         for hop in range(plan.n_hops):
             current, handle = posted[hop]
@@ -197,10 +222,10 @@ class proAttention:
                     states.append((o, l, LSE_BHS))
             self.stats["cached_blocks_merged"] += len(states)
 
-        # 2. every hop of this call is posted now, each as its own batch into its own slot: chunks
-        #    travel owner -> consumer, so the hops do not depend on one another and the link streams
-        #    them back to back while the attention kernels work through the chunks already here.
-        posted = [self._post_hop(plan, hop, payload) for hop in range(stride)] if N > 1 else [(None, None)] * stride
+        # 2. every hop of this call is posted now, each into its own slot: chunks travel owner ->
+        #    consumer, so the hops do not depend on one another and the link streams them while the
+        #    attention kernels work through the chunks already here.
+        posted = self._post_hops(plan, stride, payload) if N > 1 else [(None, None)] * stride
         own = None
         if mine.own_first:
             own = attend(payload)          # target block is a foreign one: own chunk first, overlapping hop 0

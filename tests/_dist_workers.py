@@ -37,6 +37,7 @@ def ring_worker(rank, world, port, case, ret):
     for t, d in enumerate(div):
         rm.divider_map[t, 0] = d
     layer = proAttention(0, ps.get_isp_group())
+    layer.hop_grouping = case.get("hop_grouping", "single")
     B, S, H, D = case["B"], case["S"], case["H"], case["D"]
     data = drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"])
     outs = []
@@ -177,6 +178,7 @@ def pair_worker(rank, world, port, case, ret):
     rm = init_redundancy_map(cfg)
     rm.set_pair_map(np.asarray(case["reusable"], dtype=bool)[:, None])      # [T, 1, N, N]
     layer = proAttention(0, ps.get_isp_group())
+    layer.hop_grouping = case.get("hop_grouping", "single")
     B, S, H, D = case["B"], case["S"], case["H"], case["D"]
     data = drifting_qkv(B, S, H, D, T, seed=case["seed"], drift=case["drift"])
     outs = []
