@@ -118,6 +118,7 @@ def gpu_ring_worker(rank, world, port, case, ret):
     for t, d in enumerate(div):
         rm.divider_map[t, 0] = d
     layer = proAttention(0, ps.get_isp_group())
+    layer.hop_grouping = case.get("hop_grouping", "single")
     B, S, H, D = case["B"], case["S"], case["H"], case["D"]
     data = drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"], dtype=torch.bfloat16)
     lo, hi = rank * S // world, (rank + 1) * S // world

@@ -90,11 +90,11 @@ CASES = {
 }
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_ring_attention_multi_gpu_matches_oracle(world):
+@pytest.mark.parametrize("world,grouping", [(2, "single"), (4, "single"), (8, "single"), (4, "doubling"), (8, "doubling")])
+def test_ring_attention_multi_gpu_matches_oracle(world, grouping):
     if _ngpu() < world:
         pytest.skip(f"needs {world} GPUs")
-    case = CASES[world]
+    case = dict(CASES[world], hop_grouping=grouping)
     ret = _spawn(world, case)
     data = O.drifting_qkv(case["B"], case["S"], case["H"], case["D"], len(case["dividers"]), seed=case["seed"],
                           drift=case["drift"], dtype=torch.bfloat16)
