@@ -1,6 +1,7 @@
 """Shared helpers with the reference's names (utils.py of the reference):
 the global denoising-step index (:15-21), the two-state merge `update_out_and_lse` (:24-84) and the
-zero-padded sequence sharding helpers (:86-167)."""
+zero-padded sequence sharding helpers (:86-167), plus two helpers the reference lacks that keep the pad
+tokens out of attention (`uneven_shard_cu_seqlens`) and out of the gathered result (`gather_sequence_shards`)."""
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -90,3 +91,47 @@ def remove_padding_after_gather(tensor: torch.Tensor, tensor_name: str) -> torch
         return tensor
     keep = torch.cat([torch.arange(r * seg, (r + 1) * seg - p, device=tensor.device) for r, p in enumerate(pads)])
     return tensor.index_select(1, keep)
+
+
+def uneven_shard_lengths(total_len: int, world_size: int) -> List[int]:
+    """Real tokens per shard for the split of split_tensor_uneven."""
+    base, rem = divmod(total_len, world_size)
+    return [base + (1 if i < rem else 0) for i in range(world_size)]
+
+
+def uneven_shard_cu_seqlens(total_len: int, world_size: int, rank: int, batch_size: int = 1,
+                            device=None) -> Tuple[torch.Tensor, int]:
+    """Segment table that keeps the zero pad of an uneven shard out of attention.
+
+    The reference pads short shards with zero tokens which then act as real keys in every layer
+    (utils.py:117-127; nothing masks them).  Fed to `proAttention.varlen_attn` as cu_seqlens_q and
+    cu_seqlens_kv of the packed shard `[batch * shard_len, H, D]`, this table puts each sample's real
+    tokens in one segment and its pad tokens in another, so real queries see real keys only -- the same
+    device the HunyuanVideo adapter uses for masked text (hunyuan_transformer.py:789-792).
+    Returns (int32 cu_seqlens of length 2*batch + 1, max segment length)."""
+    lengths = uneven_shard_lengths(total_len, world_size)
+    shard = max(lengths)
+    valid = lengths[rank]
+    cu = [0]
+    for b in range(batch_size):
+        cu += [b * shard + valid, (b + 1) * shard]
+    return torch.tensor(cu, dtype=torch.int32, device=device), shard
+
+
+def gather_sequence_shards(group, local: torch.Tensor, total_len: int, dim: int = 1) -> torch.Tensor:
+    """All-gather equal-length (padded) shards along `dim` and return exactly total_len positions: one
+    all_gather_into_tensor, then one narrow copy per rank that skips its pad (what
+    remove_padding_after_gather does through the name dictionary, utils.py:142-167)."""
+    world = group.world_size
+    if world == 1:
+        return local.narrow(dim, 0, total_len)
+    parts = group.all_gather(local, dim=0, split=True)
+    lengths = uneven_shard_lengths(total_len, world)
+    shape = list(local.shape)
+    shape[dim] = total_len
+    out = local.new_empty(shape)
+    start = 0
+    for part, n in zip(parts, lengths):
+        out.narrow(dim, start, n).copy_(part.narrow(dim, 0, n))
+        start += n
+    return out

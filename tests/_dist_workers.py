@@ -58,6 +58,33 @@ def ring_worker(rank, world, port, case, ret):
     dist.destroy_process_group()
 
 
+def uneven_worker(rank, world, port, case, ret):
+    """Uneven sequence shards: zero-padded as the reference does, with and without the pad masked."""
+    cfg, ps = _setup(rank, world, port)
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.utils import (gather_sequence_shards, split_tensor_uneven, uneven_shard_cu_seqlens,
+                                    update_timestep)
+    cfg.num_layers, cfg.num_inference_steps = 2, 1
+    init_redundancy_map(cfg)
+    update_timestep(0)
+    group = ps.get_isp_group()
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    g = torch.Generator().manual_seed(case["seed"])
+    q, k, v = (torch.randn(B, S, H, D, generator=g) for _ in range(3))
+    ql, kl, vl = (split_tensor_uneven(x, world, dim=1)[rank].contiguous() for x in (q, k, v))
+    shard = ql.shape[1]
+    cu, max_len = uneven_shard_cu_seqlens(S, world, rank, batch_size=B)
+    masked = proAttention(0, group).varlen_attn(ql.reshape(B * shard, H, D), kl.reshape(B * shard, H, D),
+                                                vl.reshape(B * shard, H, D), cu_seqlens_q=cu, cu_seqlens_kv=cu,
+                                                max_seqlen_q=max_len, max_seqlen_kv=max_len, batch_size=B)
+    masked = gather_sequence_shards(group, masked.reshape(B, shard, H, D), S, dim=1)
+    padded = gather_sequence_shards(group, proAttention(1, group).attn(ql, kl, vl), S, dim=1)
+    ret[rank] = (masked, padded)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def ulysses_worker(rank, world, port, case, ret):
     cfg, ps = _setup(rank, world, port)
     from ditango_b200.baseline.ulysses import ulysses_attention
@@ -139,6 +166,43 @@ def gpu_ring_worker(rank, world, port, case, ret):
         uly = ulysses_attention(ql, kl, vl, group=ps.get_isp_group()).float().cpu()
     status = ops.read_status()
     ret[rank] = (torch.stack(outs), dict(layer.stats), uly, status)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gpu_uneven_worker(rank, world, port, case, ret):
+    """NCCL ranks, real kernels: uneven shards with the pad in a segment of its own, gathered pad-free."""
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world), RANK=str(rank),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    from ditango_b200 import ops
+    from ditango_b200.core import parallel_state as ps
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core.redundancy_map import init_redundancy_map
+    from ditango_b200.utils import (gather_sequence_shards, split_tensor_uneven, uneven_shard_cu_seqlens,
+                                    update_timestep)
+    cfg = init_config(None, make_output_dir=False)
+    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=rank, backend="nccl")
+    c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+    ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+    cfg.num_layers, cfg.num_inference_steps = 1, 1
+    init_redundancy_map(cfg)
+    update_timestep(0)
+    group = ps.get_isp_group()
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    g = torch.Generator().manual_seed(case["seed"])
+    q, k, v = (torch.randn(B, S, H, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    ql, kl, vl = (split_tensor_uneven(x, world, dim=1)[rank].contiguous().cuda() for x in (q, k, v))
+    shard = ql.shape[1]
+    cu, max_len = uneven_shard_cu_seqlens(S, world, rank, batch_size=B, device="cuda")
+    out = proAttention(0, group).varlen_attn(ql.reshape(B * shard, H, D), kl.reshape(B * shard, H, D),
+                                             vl.reshape(B * shard, H, D), cu_seqlens_q=cu, cu_seqlens_kv=cu,
+                                             max_seqlen_q=max_len, max_seqlen_kv=max_len, batch_size=B)
+    out = gather_sequence_shards(group, out.reshape(B, shard, H, D), S, dim=1)
+    ret[rank] = (out.float().cpu(), ops.read_status())
     dist.barrier()
     dist.destroy_process_group()
 

@@ -127,6 +127,26 @@ def test_packed_ring_two_gpus():
             assert e.max() <= 2e-2 and e.mean() <= 1e-3
 
 
+def test_uneven_shards_with_masked_pad_two_gpus():
+    """257 tokens on 2 ranks (129 + 128 padded to 129): pad tokens sit in a segment of their own and are
+    dropped by the gather; the result is full attention over the real tokens."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    case = dict(B=2, S=257, H=2, D=128, seed=13)
+    _PORT[0] += 1
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(W.gpu_uneven_worker, args=(2, _PORT[0], case, ret), nprocs=2, join=True)
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(2, 257, 2, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+    full, _ = O.partial_attention(q, k, v, out_dtype=torch.float32)
+    for r in range(2):
+        out, status = ret[r]
+        assert status == 0
+        e = (out - full).abs()
+        assert e.max() <= 2e-2 and e.mean() <= 1e-3, (r, e.max().item(), e.mean().item())
+
+
 def test_profiling_mode_records_drift_on_device():
     """RedundancyMap in profiling mode: full stride everywhere, drift of consecutive outputs added
     to the map by the device kernel, equal to the reference's rel_l1 of those outputs."""

@@ -79,6 +79,21 @@ def test_fewer_chunks_move_than_in_a_plain_ring():
     assert ret[0][1]["chunks_attended"] < T * world
 
 
+def test_uneven_shards_with_masked_pad_equal_full_attention():
+    """66 tokens on 4 ranks: shards of 17, 17, 16, 16 padded to 17.  With the pad in a segment of its own
+    the gathered result is full attention over the 66 real tokens; the reference's unmasked zero pad is not."""
+    case = dict(B=2, S=66, H=2, D=16, seed=11)
+    ret = _spawn(W.uneven_worker, 4, case)
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(2, 66, 2, 16, generator=g) for _ in range(3))
+    full, _ = O.partial_attention(q, k, v)
+    for r in range(4):
+        masked, padded = ret[r]
+        assert masked.shape == full.shape
+        assert (masked - full).abs().max().item() <= 2e-5
+        assert (padded - full).abs().max().item() > 1e-3      # two zero keys leak into every row
+
+
 def test_ulysses_equals_full_attention_world2():
     case = dict(B=2, S=64, H=4, D=16, seed=5)
     ret = _spawn(W.ulysses_worker, 2, case)
