@@ -134,3 +134,16 @@ def test_split_and_unpad_roundtrip():
     assert all(p.shape[1] == 3 for p in parts)
     back = remove_padding_after_gather(torch.cat(parts, dim=1), "x")
     assert torch.equal(back, x)
+
+
+def test_uneven_shard_segment_table_and_single_rank_gather():
+    from ditango_b200.core.group_coordinate import SingleRankGroup
+    from ditango_b200.utils import gather_sequence_shards, uneven_shard_cu_seqlens, uneven_shard_lengths
+    assert uneven_shard_lengths(66, 4) == [17, 17, 16, 16]
+    assert uneven_shard_lengths(64, 4) == [16, 16, 16, 16]
+    cu, longest = uneven_shard_cu_seqlens(66, 4, rank=2, batch_size=2)
+    assert cu.dtype == torch.int32 and cu.tolist() == [0, 16, 17, 33, 34] and longest == 17
+    cu, _ = uneven_shard_cu_seqlens(66, 4, rank=0, batch_size=1)
+    assert cu.tolist() == [0, 17, 17]                      # no pad on this rank: empty second segment
+    x = torch.arange(24, dtype=torch.float32).view(1, 12, 2)
+    assert torch.equal(gather_sequence_shards(SingleRankGroup(torch.device("cpu")), x, 12), x)
