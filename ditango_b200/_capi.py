@@ -18,6 +18,7 @@ MERGE_MAX_STATES = 16
 
 EXPORTS = (
     "dtb_version", "dtb_last_error", "dtb_device_supported", "dtb_read_status",
+    "dtb_peek_status_async", "dtb_post_status",
     "dtb_flash_fwd", "dtb_merge_states", "dtb_copy_chunks",
     "dtb_drift_scratch_bytes", "dtb_drift_accumulate",
     "dtb_drift_noalloc_max_elements", "dtb_drift_accumulate_noalloc",
@@ -47,6 +48,10 @@ def load():
     lib.dtb_device_supported.restype = c_int
     lib.dtb_read_status.restype = c_int
     lib.dtb_read_status.argtypes = [c_void_p]
+    lib.dtb_peek_status_async.restype = c_int
+    lib.dtb_peek_status_async.argtypes = [c_void_p, c_void_p]
+    lib.dtb_post_status.restype = c_int
+    lib.dtb_post_status.argtypes = [c_int, c_void_p]
     lib.dtb_flash_fwd.restype = c_int
     lib.dtb_flash_fwd.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

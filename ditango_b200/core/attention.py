@@ -25,7 +25,7 @@ import torch
 import torch.distributed
 
 from .. import ops as _engine
-from .._capi import LSE_BHS
+from .._capi import LSE_BHS, LSE_BSH
 from ..logger import init_logger
 from ..timer import get_timer
 from ..utils import get_timestep
@@ -36,26 +36,46 @@ from .schedule import StepPlan, plan_pair_step, plan_step
 
 logger = init_logger(__name__)
 
-# One receive slot per hop and (device, shape, dtype), shared by all layers of the process: layers run
-# one after another, and a layer call has at most group-size hops in flight.
+# One receive slot per (group, hop, payload index), shared by all layers that use the group: layers run
+# one after another on ONE stream, and a layer call has at most group-size hops in flight.  Two
+# attention objects of the same group driven from different streams would race on these slots.
+# A slot follows the latest shape it was asked for; buffers of shapes no longer in use are dropped.
 _SLOTS: Dict[Tuple, torch.Tensor] = {}
 
 
-def _slot(tag: str, index: int, like: torch.Tensor) -> torch.Tensor:
-    key = (tag, index, like.device, tuple(like.shape), like.dtype)
-    if key not in _SLOTS:
-        _SLOTS[key] = torch.empty_like(like, memory_format=torch.contiguous_format)
-    return _SLOTS[key]
+def _slot(group, tag: str, index: int, like: torch.Tensor) -> torch.Tensor:
+    key = (id(group), tag, index)
+    buf = _SLOTS.get(key)
+    if buf is None or buf.shape != like.shape or buf.dtype != like.dtype or buf.device != like.device:
+        buf = torch.empty_like(like, memory_format=torch.contiguous_format)
+        _SLOTS[key] = buf
+    return buf
 
 
-def release_receive_slots():
-    _SLOTS.clear()
+def release_receive_slots(group=None):
+    """Drop the receive buffers of `group` (all groups when None)."""
+    if group is None:
+        _SLOTS.clear()
+        return
+    for key in [k for k in _SLOTS if k[0] == id(group)]:
+        del _SLOTS[key]
+
+
+# Denoising step at which the device status word was last polled by this process (see _run).
+_STATUS_POLL = {"step": None}
 
 
 class proAttention:
     # How the hops of one call are batched for the transport ("single" or "doubling", see _post_hops).
     # Class-wide default; every rank of a group must agree.
     hop_grouping = "single"
+    # dtype of the returned tensor.  float32 is the reference's contract (its callers cast to bf16 right
+    # away: executor/cogvideox/attention_processor.py:80, executor/step/attentions.py:98); with
+    # torch.bfloat16 the cast is fused into the last kernel of the call and the fp32 copy is never written.
+    output_dtype = torch.float32
+    # dtype of the values of cached block states (the reference keeps fp32: utils.py:76); bfloat16 halves
+    # the cache's footprint and read traffic.  lse stays fp32.
+    cache_dtype = torch.float32
 
     def __init__(self, layer_id: int, isp_group):
         self.group = isp_group
@@ -66,8 +86,16 @@ class proAttention:
         self.target_chunk_id = 0
         # chunk pointer of every rank of the group for this layer; all ranks keep the same copy
         self._pointers = [0] * self.isp_size
-        self.cache = proCache(isp_size=self.isp_size, layer_id=layer_id)
         cfg = get_config()
+        if cfg is not None and getattr(cfg, "cache_dtype", None) in ("bf16", "bfloat16"):
+            self.cache_dtype = torch.bfloat16
+        if cfg is not None and getattr(cfg, "output_dtype", None) in ("bf16", "bfloat16"):
+            self.output_dtype = torch.bfloat16
+        # Partial states, cached states and their merges keep lse as [B,S,H] ([T,H] packed): one lse per
+        # (token, head) row in the order the value rows are stored, so the merge kernel reads it without
+        # index arithmetic.  Only `last_lse` is presented as [B,H,S], what flash_attn returns.
+        self.cache = proCache(isp_size=self.isp_size, layer_id=layer_id, store_dtype=self.cache_dtype,
+                              lse_layout=LSE_BSH)
         self.use_ditango = bool(cfg.use_ditango) if cfg is not None else True
         self.small_ring_stride = 8
         self.measure_memory = False
@@ -76,10 +104,34 @@ class proAttention:
         # chunks every rank of the group holds (all ranks keep the same copy)
         self._chunk_states: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._have = [set() for _ in range(self.isp_size)]
-        self.last_lse: Optional[torch.Tensor] = None       # [B,H,S] / [H,T] of the last result
+        self._last_lse: Optional[torch.Tensor] = None      # [B,S,H] / [T,H] of the last result
         self.stats = dict(calls=0, chunks_attended=0, chunks_received=0, bytes_received=0,
                           cached_blocks_merged=0, merge_launches=0)
         self._comm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
+
+    @property
+    def last_lse(self) -> Optional[torch.Tensor]:
+        """Log-sum-exp of the last result as [B,H,S] (packed: [H,T]), the layout flash_attn returns."""
+        return None if self._last_lse is None else self._last_lse.transpose(-1, -2)
+
+    def _finish(self, own, others):
+        """Combine the own-chunk state with all other states of the call into the result: one merge launch
+        (in place in the own state's fp32 buffer), or none when there is nothing to merge."""
+        want_bf16 = self.output_dtype == torch.bfloat16
+        if others:
+            res16 = torch.empty(own[0].shape, dtype=torch.bfloat16, device=own[0].device) if want_bf16 else None
+            out, lse = _engine.merge_states([(own[0], own[1], LSE_BSH)] + others, out=own[0], lse_out=own[1],
+                                            lse_out_layout=LSE_BSH, out_bf16=res16, fp32_out=not want_bf16)
+            self.stats["merge_launches"] += 1
+            return (res16 if want_bf16 else out), lse
+        out, lse = own
+        if want_bf16 and out.dtype != torch.bfloat16:
+            # every chunk was folded into the fp32 state by the attention kernel: one cast pass
+            res16 = torch.empty(out.shape, dtype=torch.bfloat16, device=out.device)
+            _engine.merge_states([(out, lse, LSE_BSH)], out=out, want_lse=False, out_bf16=res16, fp32_out=False)
+            self.stats["merge_launches"] += 1
+            out = res16
+        return out, lse
 
     # ------------------------------------------------------------------ transport
     def _queue_hop(self, plan: StepPlan, hop: int, payload: Tuple[torch.Tensor, ...]):
@@ -92,7 +144,7 @@ class proAttention:
             for t in payload:
                 self.group.p2p_isend(t, dst=dst)
         if src is not None:
-            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(f"kv{i}", hop, t)) for i, t in enumerate(payload))
+            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(self.group, f"kv{i}", hop, t)) for i, t in enumerate(payload))
             self.stats["chunks_received"] += 1
             self.stats["bytes_received"] += sum(t.numel() * t.element_size() for t in payload)
         return recv
@@ -146,12 +198,13 @@ class proAttention:
         packed = cu_q is not None
         payload = (key, value, cu_kv) if packed else (key, value)
 
-        def attend(kv):
+        def attend(kv, keep=False):
             kw = {}
             if packed:
                 kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
             self.stats["chunks_attended"] += 1
-            return _engine.flash_partial(query, kv[0], kv[1], lse_layout=LSE_BHS, **kw)
+            return _engine.flash_partial(query, kv[0], kv[1], lse_layout=LSE_BSH,
+                                         out_dtype=self.cache_dtype if keep else torch.float32, **kw)
 
         plan = plan_pair_step(N, flags, self._have)
         posted = self._post_hops(plan, plan.n_hops, payload)
@@ -160,17 +213,12 @@ class proAttention:
             current, handle = posted[hop]
             self._wait_hop(handle)
             if current is not None:
-                self._chunk_states[plan.ranks[me].owners[hop]] = attend(current)
-        others = [(o, l, LSE_BHS) for src in ((me + i) % N for i in range(1, N))
+                self._chunk_states[plan.ranks[me].owners[hop]] = attend(current, keep=True)
+        others = [(o, l, LSE_BSH) for src in ((me + i) % N for i in range(1, N))
                   for o, l in (self._chunk_states.get(src, (None, None)),) if l is not None]
         self.stats["cached_blocks_merged"] += len(others) - len(plan.ranks[me].owners)
-        if others:
-            out, lse = _engine.merge_states([(own[0], own[1], LSE_BHS)] + others, out=own[0], lse_out=own[1],
-                                            lse_out_layout=LSE_BHS)
-            self.stats["merge_launches"] += 1
-        else:
-            out, lse = own
-        self.last_lse = lse
+        out, lse = self._finish(own, others)
+        self._last_lse = lse
         self.stats["calls"] += 1
         return out
 
@@ -179,6 +227,13 @@ class proAttention:
         N, me = self.isp_size, self.local_chunk_id
         rmap = get_redundancy_map()
         t = get_timestep()
+        if _STATUS_POLL["step"] != t:
+            # Once per denoising step: a kernel whose bounded wait ran out leaves a sticky code in the
+            # device status word and every later launch skips its work, so results from then on would be
+            # garbage behind a zero return code.  The poll never blocks: it tests the copy made one
+            # step earlier and queues the next one.
+            _STATUS_POLL["step"] = t
+            _engine.poll_status()
         flags = rmap.pair_flags(t, self.layer_id) if N > 1 else None
         if flags is not None:
             return self._run_pairs(flags, query, key, value, cu_q, cu_kv, max_q, max_kv)
@@ -202,16 +257,16 @@ class proAttention:
         keep_chunks = stride == N and next_stride != N        # fine-grained store after a full refresh
         keep_block = stride != N and next_stride != N
 
-        def attend(kv, into=None):
+        def attend(kv, into=None, dtype=torch.float32):
             kk, vv = kv[0], kv[1]
             kw = {}
             if packed:
                 kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
             self.stats["chunks_attended"] += 1
             if into is None:
-                return _engine.flash_partial(query, kk, vv, lse_layout=LSE_BHS, **kw)
+                return _engine.flash_partial(query, kk, vv, lse_layout=LSE_BSH, out_dtype=dtype, **kw)
             return _engine.flash_partial(query, kk, vv, out=into[0], lse=into[1], accumulate=True,
-                                         lse_layout=LSE_BHS, **kw)
+                                         lse_layout=LSE_BSH, **kw)
 
         # 1. cached blocks (every block but the target one)
         states = []
@@ -219,51 +274,49 @@ class proAttention:
             for i in range(nblk - 1):
                 o, l = self.cache.get_block((mine.target_block + 1 + i) % nblk)
                 if l is not None:
-                    states.append((o, l, LSE_BHS))
+                    states.append((o, l, LSE_BSH))
             self.stats["cached_blocks_merged"] += len(states)
 
         # 2. every hop of this call is posted now, each into its own slot: chunks travel owner ->
         #    consumer, so the hops do not depend on one another and the link streams them while the
         #    attention kernels work through the chunks already here.
         posted = self._post_hops(plan, stride, payload) if N > 1 else [(None, None)] * stride
+        # A single rank with nothing to merge gets its bf16 result straight from the attention kernel.
+        direct16 = N == 1 and self.output_dtype == torch.bfloat16 and not rmap.is_auto_setting()
         own = None
         if mine.own_first:
             own = attend(payload)          # target block is a foreign one: own chunk first, overlapping hop 0
 
-        # 3. the target block's chunks
+        # 3. the target block's chunks.  A state that goes to the cache without further accumulation is
+        #    written by the attention kernel in the cache's dtype: no cast pass afterwards.
         fresh = None
         chunk_states = []
+        fresh_chunks = sum(1 for o in mine.owners if o != me)
         for hop in range(stride):
             current, handle = posted[hop]
             self._wait_hop(handle)
             if mine.owners[hop] == me:
-                own = attend(payload)
+                own = attend(payload, dtype=torch.bfloat16 if direct16 else torch.float32)
             elif keep_chunks:
-                st = attend(current)
+                st = attend(current, dtype=self.cache_dtype)
                 self.cache.store_block(mine.owners[hop], st[0], st[1])
-                chunk_states.append((st[0], st[1], LSE_BHS))
+                chunk_states.append((st[0], st[1], LSE_BSH))
             elif keep_block:
-                fresh = attend(current, into=fresh)
+                fresh = attend(current, into=fresh, dtype=self.cache_dtype if fresh_chunks == 1 else torch.float32)
             else:
                 own = attend(current, into=own)          # nothing is kept: fold into the result
 
         # 4. store the fresh block, combine everything in one pass
         if fresh is not None:
             self.cache.store_block(mine.target_block, fresh[0], fresh[1])
-            chunk_states.append((self.cache.out_block_cache[mine.target_block], fresh[1], LSE_BHS))
-        others = states + chunk_states
-        if others:
-            out, lse = _engine.merge_states([(own[0], own[1], LSE_BHS)] + others, out=own[0], lse_out=own[1],
-                                            lse_out_layout=LSE_BHS)
-            self.stats["merge_launches"] += 1
-        else:
-            out, lse = own
+            chunk_states.append((self.cache.out_block_cache[mine.target_block], fresh[1], LSE_BSH))
+        out, lse = self._finish(own, states + chunk_states)
 
         # 5. pointers and cache layout for the next step
         self._pointers = plan.pointers_after
         self.target_chunk_id = self._pointers[me]
         self.cache.update_cache_blocks(next_stride, self.target_chunk_id // next_stride)
-        self.last_lse = lse
+        self._last_lse = lse
         self.stats["calls"] += 1
         rmap.record_out_redundancy(timestep=t, layer_id=self.layer_id, curr_out=out)
         return out

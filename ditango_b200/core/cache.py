@@ -29,12 +29,14 @@ def _device_total_mb() -> float:
 
 
 class proCache:
-    def __init__(self, isp_size: int, layer_id: int, store_dtype: torch.dtype = torch.float32):
+    def __init__(self, isp_size: int, layer_id: int, store_dtype: torch.dtype = torch.float32,
+                 lse_layout: int = LSE_BHS):
         self.isp_size = isp_size
         self.curr_isp_stride = isp_size
         self.curr_block_num = isp_size
         self.layer_id = layer_id
         self.store_dtype = store_dtype
+        self.lse_layout = lse_layout          # layout of every lse handed to store_block ([B,H,S] or [B,S,H])
         self.out_block_cache: List[Optional[torch.Tensor]] = [None] * isp_size
         self.lse_block_cache: List[Optional[torch.Tensor]] = [None] * isp_size
         self.block_size_mb: Optional[float] = None
@@ -65,15 +67,20 @@ class proCache:
         outs: List[Optional[torch.Tensor]] = [None] * new_block_num
         lses: List[Optional[torch.Tensor]] = [None] * new_block_num
         for i in range(new_block_num):
-            members = [(self.out_block_cache[j], self.lse_block_cache[j], LSE_BHS)
+            members = [(self.out_block_cache[j], self.lse_block_cache[j], self.lse_layout)
                        for j in range(i * per, (i + 1) * per) if self.lse_block_cache[j] is not None]
             if not members:
                 continue
             if len(members) == 1:
                 outs[i], lses[i] = members[0][0], members[0][1]
                 continue
-            o, l = _engine.merge_states(members, lse_out_layout=LSE_BHS)
-            outs[i], lses[i] = (o if o.dtype == self.store_dtype else o.to(self.store_dtype)), l
+            if self.store_dtype == torch.bfloat16:
+                # the merged block leaves the kernel as bf16; no fp32 copy is written
+                o = torch.empty(members[0][0].shape, dtype=torch.bfloat16, device=members[0][0].device)
+                _, l = _engine.merge_states(members, lse_out_layout=self.lse_layout, out_bf16=o, fp32_out=False)
+            else:
+                o, l = _engine.merge_states(members, lse_out_layout=self.lse_layout)
+            outs[i], lses[i] = o, l
         self.out_block_cache, self.lse_block_cache = outs, lses
 
     def update_cache_blocks(self, new_isp_stride: int, next_target_block_id: int):

@@ -36,6 +36,9 @@ class RedundancyMap:
         self.redundancy_map: Optional[torch.Tensor] = None
         self._divider_map = self._init_map()
         self._table = None
+        self._table_version = -1
+        self._device_map = None          # [T,L] fp32 on the GPU while profiling there
+        self.pair_reuse = None           # per-pair reuse map, see set_pair_map
 
     # The divider map stays a torch long tensor, as callers of the reference index and assign it
     # directly (`rm.divider_map[t, l] = d`); the int lookup table is rebuilt lazily after writes.
@@ -70,14 +73,19 @@ class RedundancyMap:
 
     def pair_flags(self, timestep: int, layer_id: int):
         """reusable[src][dst] of one cell as nested lists, or None when the stride schedule is active."""
-        pr = getattr(self, "pair_reuse", None)
+        pr = self.pair_reuse
         if pr is None or self.auto_setting:
             return None
         return pr[timestep, layer_id].tolist()
 
     def _dividers(self) -> List[List[int]]:
-        if self._table is None:
+        # The table is rebuilt after any in-place write to the tensor, whichever alias the caller wrote
+        # through (`rm.divider_map[t, l] = d`, `rm.get_map()[t, l] = d`, a reference kept from earlier):
+        # torch counts in-place writes per tensor.  In the reference every lookup reads the tensor.
+        version = self._divider_map._version
+        if self._table is None or self._table_version != version:
             self._table = self._divider_map.tolist()
+            self._table_version = version
         return self._table
 
     def is_auto_setting(self) -> bool:
@@ -220,6 +228,8 @@ class RedundancyMap:
         back by finish_auto_setting()."""
         if not self.auto_setting:
             return
+        if self.redundancy_map is None:      # auto_setting switched on by assignment, as reference-era code may
+            self.redundancy_map = torch.zeros(self.num_timesteps, self.num_layers, dtype=torch.float)
         prev = self.prev_out[layer_id]
         if prev is not None:
             if curr_out.is_cuda:
@@ -229,12 +239,12 @@ class RedundancyMap:
                                                    device=curr_out.device)
                 ops.drift_accumulate(curr_out.float(), prev.float(), self._device_map[timestep, layer_id])
             else:
-                d = (curr_out.double() - prev.double()).abs().mean() / (prev.double().abs().mean() + 1e-8)
-                self.redundancy_map[timestep, layer_id] += float(d)
+                from ..utils import rel_l1
+                self.redundancy_map[timestep, layer_id] += rel_l1(curr_out, prev)
         self.prev_out[layer_id] = curr_out
 
     def _collect_device_map(self):
-        if getattr(self, "_device_map", None) is not None:
+        if self._device_map is not None:
             self.redundancy_map = self.redundancy_map + self._device_map.cpu()
             self._device_map = None
 

@@ -31,6 +31,9 @@ int fail(int code, const char* fmt, ...) {
 // Device status word written by kernels whose bounded waits ran out.
 __device__ int g_status_word;
 
+// First code wins, as for codes reported by the kernels themselves.
+__global__ void post_status_kernel(int* word, int code) { atomicCAS(word, 0, code); }
+
 struct DeviceInfo {
   bool probed = false;
   int cc_major = 0;
@@ -151,6 +154,27 @@ DTB_API int dtb_read_status(void* stream) {
   return host;
 }
 
+DTB_API int dtb_peek_status_async(int* host_word, void* stream) {
+  if (!host_word) return fail(DTB_ERR_ARG, "dtb_peek_status_async: null destination");
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != DTB_OK) return rc;
+  cudaError_t e = cudaMemcpyAsync(host_word, d->status_ptr, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "status copy failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
+DTB_API int dtb_post_status(int code, void* stream) {
+  if (code <= 0) return fail(DTB_ERR_ARG, "dtb_post_status: code must be positive, got %d", code);
+  DeviceInfo* d = nullptr;
+  int rc = device_info(&d);
+  if (rc != DTB_OK) return rc;
+  post_status_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(d->status_ptr, code);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "status write failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
 DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
                   int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
                   void* out, int out_dtype, int64_t out_tok_stride,
@@ -219,7 +243,8 @@ DTB_API int dtb_merge_states(int nstates, const void* const* outs, const int* ou
                      int batch, int seq, int num_heads, int head_dim, void* stream) {
   if (nstates < 1 || nstates > DTB_MERGE_MAX_STATES) return fail(DTB_ERR_ARG, "dtb_merge_states: nstates %d not in [1, %d]", nstates, DTB_MERGE_MAX_STATES);
   if (head_dim != 64 && head_dim != 128) return fail(DTB_ERR_ARG, "dtb_merge_states: head_dim %d not in {64, 128}", head_dim);
-  if (!outs || !out_dtypes || !lses || !lse_layouts || !out) return fail(DTB_ERR_ARG, "dtb_merge_states: null argument");
+  if (!outs || !out_dtypes || !lses || !lse_layouts) return fail(DTB_ERR_ARG, "dtb_merge_states: null argument");
+  if (!out && !out_bf16) return fail(DTB_ERR_ARG, "dtb_merge_states: neither an fp32 nor a bf16 result buffer was given");
   if (batch < 0 || seq < 0 || num_heads < 1) return fail(DTB_ERR_ARG, "dtb_merge_states: bad shape");
   DeviceInfo* d = nullptr;
   int rc = device_info(&d);
@@ -231,15 +256,15 @@ DTB_API int dtb_merge_states(int nstates, const void* const* outs, const int* ou
     if (!aligned16(outs[i])) return fail(DTB_ERR_ARG, "dtb_merge_states: state %d is not 16-byte aligned", i);
     if (out_dtypes[i] != DTB_F32 && out_dtypes[i] != DTB_BF16) return fail(DTB_ERR_ARG, "dtb_merge_states: bad dtype for state %d", i);
     if (lse_layouts[i] != DTB_LSE_BHS && lse_layouts[i] != DTB_LSE_BSH) return fail(DTB_ERR_ARG, "dtb_merge_states: bad lse layout for state %d", i);
-    if (i > 0 && (outs[i] == out || (lse_out && lses[i] == lse_out))) return fail(DTB_ERR_ARG, "dtb_merge_states: the result may alias state 0 only");
+    if (i > 0 && ((out && outs[i] == out) || (lse_out && lses[i] == lse_out))) return fail(DTB_ERR_ARG, "dtb_merge_states: the result may alias state 0 only");
     p.outs[i] = outs[i];
     p.lse[i] = lses[i];
     p.out_dtype[i] = out_dtypes[i];
     p.lse_layout[i] = lse_layouts[i];
   }
-  if (outs[0] == out && out_dtypes[0] != DTB_F32) return fail(DTB_ERR_ARG, "dtb_merge_states: in-place merge needs an fp32 state 0");
+  if (out && outs[0] == out && out_dtypes[0] != DTB_F32) return fail(DTB_ERR_ARG, "dtb_merge_states: in-place merge needs an fp32 state 0");
   if (lse_out && lses[0] == lse_out && lse_layouts[0] != lse_out_layout) return fail(DTB_ERR_ARG, "dtb_merge_states: in-place lse needs matching layouts");
-  if (!aligned16(out) || (out_bf16 && !aligned16(out_bf16))) return fail(DTB_ERR_ARG, "dtb_merge_states: result not 16-byte aligned");
+  if ((out && !aligned16(out)) || (out_bf16 && !aligned16(out_bf16))) return fail(DTB_ERR_ARG, "dtb_merge_states: result not 16-byte aligned");
   p.out = out;
   p.lse_out = lse_out;
   p.out_bf16 = static_cast<uint16_t*>(out_bf16);

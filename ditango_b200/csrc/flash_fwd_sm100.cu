@@ -33,6 +33,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 namespace dtb {
 
 namespace {
@@ -776,12 +778,16 @@ cudaError_t launch_flash(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
                          cudaStream_t stream) {
   using C = Cfg<D>;
   static bool configured[64] = {};
+  static std::mutex mu;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
   }
   dim3 grid((p.seqlen_q + kQT * kBM - 1) / (kQT * kBM), p.num_heads, p.nseg);
   flash_fwd_kernel<D><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);

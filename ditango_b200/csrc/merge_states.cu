@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(128) merge_states_kernel(const MergeParams p) 
       const int64_t row = base + u;
       if (row < p.rows) {
         const int64_t off = row * D + lane_in_group * 4;
-        st_f4(p.out + off, acc[u]);
+        if (p.out != nullptr) st_f4(p.out + off, acc[u]);
         if (p.out_bf16 != nullptr) st_bf4(p.out_bf16 + off, acc[u]);
         if (p.lse_out != nullptr && lane_in_group == 0)
           p.lse_out[lse_offset(p.lse_out_layout, static_cast<uint32_t>(row), p.H, p.S)] = lse_out[u];
@@ -158,7 +158,13 @@ static cudaError_t launch_merge_cfg(const MergeParams& p, int G, int sm_count, c
   constexpr int kThreads = 128;
   const int64_t groups_needed = (p.rows + U - 1) / U;
   const int64_t blocks_needed = (groups_needed * G + kThreads - 1) / kThreads + 1;
-  const int64_t cap = static_cast<int64_t>(sm_count) * 7;      // resident CTAs of 128 threads per SM at ~70 registers
+  // one resident wave: CTAs per SM as the occupancy calculator reports them for this instantiation
+  int per_sm = 0;
+  cudaError_t oe = (G == 16)
+      ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, merge_states_kernel<16, U, CH>, kThreads, 0)
+      : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, merge_states_kernel<32, U, CH>, kThreads, 0);
+  if (oe != cudaSuccess || per_sm < 1) per_sm = 6;
+  const int64_t cap = static_cast<int64_t>(sm_count) * per_sm;
   int blocks = static_cast<int>(blocks_needed < cap ? blocks_needed : cap);
   if (blocks < 1) blocks = 1;
   if (G == 16)
@@ -169,10 +175,14 @@ static cudaError_t launch_merge_cfg(const MergeParams& p, int G, int sm_count, c
 }
 
 // Rows per thread x states per fetch are chosen so that about eight 16-byte loads are outstanding
-// per thread whatever the number of states.
+// per thread whatever the number of states: 4 rows x 2 states, 3 x 3, or 2 x 4.
 cudaError_t launch_merge(const MergeParams& p, int head_dim, int sm_count, cudaStream_t stream) {
   const int G = head_dim / 4;
   if (p.rows >= (1ll << 31)) return cudaErrorInvalidValue;
+#ifndef DTB_MERGE_FIXED_CFG
+  if (p.nstates <= 2) return launch_merge_cfg<4, 2>(p, G, sm_count, stream);
+  if (p.nstates == 3) return launch_merge_cfg<3, 3>(p, G, sm_count, stream);
+#endif
   return launch_merge_cfg<2, 4>(p, G, sm_count, stream);
 }
 

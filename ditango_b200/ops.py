@@ -53,6 +53,42 @@ def read_status() -> int:
     return _capi.load().dtb_read_status(_stream_ptr())
 
 
+_STATUS_WATCH = {}      # device index -> [pinned int32 word, event behind the copy in flight or None]
+
+
+def poll_status():
+    """Non-blocking look at the device status word, for the hot path.  Each call tests the copy of
+    the word that the previous call queued (if it has landed) and queues the next copy behind the
+    work already on the current stream; it raises ExtensionError when a kernel reported that a bounded
+    wait ran out -- from that point on launches skip their work and results are not valid.  The
+    report therefore comes at most one poll late.  `read_status()` clears the word."""
+    lib = _capi.load()
+    dev = torch.cuda.current_device()
+    watch = _STATUS_WATCH.get(dev)
+    if watch is None:
+        watch = _STATUS_WATCH[dev] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
+    host, pending = watch
+    if pending is not None:
+        if not pending.query():
+            return                       # the earlier copy is still behind queued work
+        watch[1] = None
+        code = int(host[0])
+        if code != 0:
+            raise _capi.ExtensionError(
+                f"a kernel gave up on a bounded wait (device status {code}); launches since then skipped "
+                "their work -- results are not valid; read_status() clears the word")
+    _capi.check(lib.dtb_peek_status_async(host.data_ptr(), _stream_ptr()), "dtb_peek_status_async")
+    ev = torch.cuda.Event()
+    ev.record()
+    watch[1] = ev
+
+
+def post_status(code: int):
+    """Set the device status word from the host (ordered on the current stream): kernels in flight give
+    up their bounded waits and later launches skip their work until read_status() clears it."""
+    _capi.check(_capi.load().dtb_post_status(int(code), _stream_ptr()), "dtb_post_status")
+
+
 def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                   out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
                   accumulate: bool = False, out_dtype: torch.dtype = torch.float32,
@@ -125,9 +161,10 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
 def merge_states(states: Sequence[Tuple[torch.Tensor, torch.Tensor, int]], *,
                  out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None,
                  lse_out_layout: int = LSE_BSH, out_bf16: Optional[torch.Tensor] = None,
-                 want_lse: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                 want_lse: bool = True, fp32_out: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """One-pass merge of partial states.  states[i] = (out_i [B,S,H,D] fp32|bf16 contiguous,
-    lse_i fp32 contiguous, layout_i).  Returns (out fp32 [B,S,H,D], lse_out or None)."""
+    lse_i fp32 contiguous, layout_i).  Returns (out fp32 [B,S,H,D], lse_out or None).  With
+    fp32_out=False only the bf16 copy `out_bf16` is written and returned in place of `out`."""
     lib = _capi.load()
     n = len(states)
     o0 = states[0][0]
@@ -148,18 +185,28 @@ def merge_states(states: Sequence[Tuple[torch.Tensor, torch.Tensor, int]], *,
         outs[i], lses[i] = o.data_ptr(), l.data_ptr()
         dts[i] = DTB_F32 if o.dtype == torch.float32 else DTB_BF16
         lays[i] = lay
-    if out is None:
+    if not fp32_out:
+        if out_bf16 is None:
+            raise _capi.ExtensionError("fp32_out=False needs out_bf16")
+        out = None
+    elif out is None:
         out = torch.empty(o0.shape, dtype=torch.float32, device=o0.device)
+    if out_bf16 is not None and (out_bf16.dtype != torch.bfloat16 or out_bf16.shape != o0.shape
+                                 or not out_bf16.is_contiguous()):
+        raise _capi.ExtensionError("out_bf16 must be a contiguous bfloat16 tensor of the states' shape")
+    if not want_lse:
+        lse_out = None
     if want_lse and lse_out is None:
         shape = ((B, S, H) if lse_out_layout == LSE_BSH else (B, H, S)) if o0.dim() == 4 else \
                 ((S, H) if lse_out_layout == LSE_BSH else (H, S))
         lse_out = torch.empty(shape, dtype=torch.float32, device=o0.device)
     rc = lib.dtb_merge_states(
-        n, outs, dts, lses, lays, out.data_ptr(), lse_out.data_ptr() if lse_out is not None else None,
+        n, outs, dts, lses, lays, out.data_ptr() if out is not None else None,
+        lse_out.data_ptr() if lse_out is not None else None,
         lse_out_layout, out_bf16.data_ptr() if out_bf16 is not None else None, B, S, H, D, _stream_ptr())
     _capi.check(rc, "dtb_merge_states")
     LaunchLog.count += 1
-    return out, lse_out
+    return (out if out is not None else out_bf16), lse_out
 
 
 def copy_chunks(pairs: Sequence[Tuple[torch.Tensor, torch.Tensor]], chunk_bytes: int,

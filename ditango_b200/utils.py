@@ -51,6 +51,23 @@ def update_out_and_lse(out: Optional[torch.Tensor], lse: Optional[torch.Tensor],
     return new_out, new_lse.unsqueeze(-1)
 
 
+def rel_l1(new_tensor: torch.Tensor, ori_tensor: torch.Tensor) -> float:
+    """Relative L1 drift of `new_tensor` against `ori_tensor` with the reference's conventions
+    (utils.py:202-267): positions where either value is NaN are left out; mean|new - ori| /
+    (mean|ori| + 1e-8); mean|new| when mean|ori| < 1e-6; +inf when no position is valid or the
+    result is not finite.  Host-side form for tensors that live on the CPU (profiling on gloo ranks);
+    on a GPU the profiling pass uses the device kernel behind ops.drift_accumulate instead."""
+    valid = ~(torch.isnan(new_tensor) | torch.isnan(ori_tensor))
+    if not bool(valid.any()):
+        return float("inf")
+    n, o = new_tensor[valid].double(), ori_tensor[valid].double()
+    ori_mean = float(o.abs().mean())
+    if ori_mean < 1e-6:
+        return float(n.abs().mean())
+    val = float((n - o).abs().mean()) / (ori_mean + 1e-8)
+    return val if val == val and val not in (float("inf"), float("-inf")) else float("inf")
+
+
 def split_tensor_uneven(tensor: torch.Tensor, world_size: int, dim: int = 1,
                         tensor_name: Optional[str] = None) -> List[torch.Tensor]:
     """Split `dim` into world_size shards of equal length ceil(len/world_size); the first

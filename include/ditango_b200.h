@@ -59,6 +59,24 @@ DTB_API int dtb_device_supported(void);
 DTB_API int dtb_read_status(void* stream);
 
 /*
+ * The word is sticky: once a wait has run out, every later launch of these kernels sees a non-zero
+ * word in its prologue and returns without doing its work, so that nothing runs on a pipeline whose
+ * state is unknown -- and nothing is stored, so results from then on are not valid although every
+ * launch call returns 0.  A caller must therefore look at the word, either with dtb_read_status at a
+ * point where a synchronisation is acceptable, or without blocking: dtb_peek_status_async queues a
+ * copy of the word into *host_word (pinned host memory, owned by the caller) on `stream`; the value
+ * is valid once work queued before the call on that stream has completed (an event recorded behind
+ * it has fired).  The reference has no counterpart; its failure mode for a stuck transfer is a hung
+ * process (core/group_coordinate.py:664-668 waits without a limit).
+ *
+ * dtb_post_status lets the host set the word (code > 0), ordered on `stream`: a watchdog that learnt
+ * on the host that a peer rank is gone uses it to make kernels in flight give up their waits (they
+ * poll the word) and to stop later launches, instead of letting each wait run to its limit.
+ */
+DTB_API int dtb_peek_status_async(int* host_word, void* stream);
+DTB_API int dtb_post_status(int code, void* stream);
+
+/*
  * Partial attention state of a query chunk against ONE key/value chunk (non-causal, no dropout):
  *     S = scale * Q K^T,  lse = logsumexp_k S,  out = softmax_k(S) V
  * Replaces flash_attn_func(q, k, v, dropout_p=0, return_attn_probs=True) at
@@ -99,9 +117,9 @@ DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
  *  outs[i]       state i's values, [rows_bs, H, D] contiguous, dtype out_dtypes[i]
  *  lses[i]       state i's fp32 lse over the same tokens, layout lse_layouts[i]
  *  out / lse_out fp32 results (lse_out may be NULL); `out` and `lse_out` may alias input 0 only.
- *  out_bf16      optional second copy of the result in bf16 (NULL to skip): the cast the
- *                reference's callers apply right after the call
- *                (executor/cogvideox/attention_processor.py:80).
+ *  out_bf16      optional copy of the result in bf16 (NULL to skip): the cast the reference's
+ *                callers apply right after the call (executor/cogvideox/attention_processor.py:80).
+ *                When it is given, `out` may be NULL and the fp32 result is not written at all.
  *  batch, seq    tokens are [batch, seq]; they matter for DTB_LSE_BHS indexing only.
  *  States whose lse is -inf on a row contribute nothing; a row empty in all states gets
  *  out = 0, lse = -inf.

@@ -35,12 +35,19 @@ def flash_partial(q, k, v, *, out=None, lse=None, accumulate=False, out_dtype=to
     return o.to(out_dtype), res_l.contiguous()
 
 
-def merge_states(states, *, out=None, lse_out=None, lse_out_layout=LSE_BSH, out_bf16=None, want_lse=True):
+def merge_states(states, *, out=None, lse_out=None, lse_out_layout=LSE_BSH, out_bf16=None, want_lse=True,
+                 fp32_out=True):
     o = l = None
     for so, sl, lay in states:
         o, l = O.merge_states(o, l, so.clone(), _to_bhs(sl, lay).clone())
     l = l.squeeze(-1)                            # [..,S,H]
     res_l = l if lse_out_layout == LSE_BSH else l.transpose(-1, -2)
+    if not fp32_out:
+        out_bf16.copy_(o.to(torch.bfloat16))
+        if lse_out is not None:
+            lse_out.copy_(res_l)
+            res_l = lse_out
+        return out_bf16, (res_l.contiguous() if want_lse else None)
     if out is not None:
         out.copy_(o)
         o = out
@@ -66,13 +73,28 @@ def copy_chunks(pairs, chunk_bytes, extents, src_strides, dst_strides):
                     db[do:do + chunk_bytes] = sb[so:so + chunk_bytes]
 
 
-def install():
-    """Point every module of the package that launches kernels at this stand-in."""
-    import sys
-    me = sys.modules[__name__]
+def poll_status():
+    return None
+
+
+def _modules():
     import ditango_b200.core.attention as A
     import ditango_b200.core.cache as C
     import ditango_b200.utils as U
     import ditango_b200.baseline.ulysses as UL
-    for m in (A, C, U, UL):
+    return (A, C, U, UL)
+
+
+def install():
+    """Point every module of the package that launches kernels at this stand-in."""
+    import sys
+    me = sys.modules[__name__]
+    for m in _modules():
         m._engine = me
+
+
+def uninstall():
+    """Point them back at the kernel wrappers (for test processes that also run GPU tests)."""
+    import ditango_b200.ops as real
+    for m in _modules():
+        m._engine = real

@@ -49,14 +49,24 @@ def test_no_alloc_entry_matches_the_scratch_entry_on_two_calls_in_a_row():
     got = torch.zeros(2, device="cuda")
     for i, (cur, prev) in enumerate(cases):
         _with_scratch(lib, cur, prev, want[i:i + 1])
-    before = torch.cuda.memory_allocated()
+    # Free device memory as the driver reports it: an allocation made inside the library would show
+    # here, which torch's own allocator statistics cannot see.  The first call on a device only looks
+    # up the address of the built-in array, so it is made before the measurement.
+    _no_alloc(lib, *cases[0], torch.zeros(1, device="cuda"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
     for i, (cur, prev) in enumerate(cases):
         _no_alloc(lib, cur, prev, got[i:i + 1])
-    assert torch.cuda.memory_allocated() == before
     torch.cuda.synchronize()
-    # same kernel, same reduction order: the tolerance of the drift tests (2e-6 relative) is ample
-    for w, g_ in zip(want.cpu().tolist(), got.cpu().tolist()):
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    # same kernel, same reduction order: the tolerance of the drift tests (2e-6 relative) is ample;
+    # and both agree with the CPU restatement of the reference's rel_l1
+    from oracle import ring_oracle as O
+    for (cur, prev), w, g_ in zip(cases, want.cpu().tolist(), got.cpu().tolist()):
         assert w > 0 and abs(w - g_) <= 2e-6 * max(1.0, abs(w))
+        ref = O.rel_l1(cur.cpu(), prev.cpu())
+        assert abs(g_ - ref) <= 2e-6 * max(1.0, abs(ref))
     # a third call accumulates on top, like the scratch entry does
     _no_alloc(lib, *cases[0], got[0:1])
     assert abs(got[0].item() - 2 * want[0].item()) <= 4e-6 * max(1.0, want[0].item())
