@@ -158,11 +158,68 @@ def step_inputs(raw, gen, w, first):
     return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
 
 
+# Miniature parity cases per group size: schedules that walk through full refresh, every divider the
+# group size admits, re-blocking and the return to full stride.
+PARITY_CASES = {
+    2: dict(B=1, S=1024, H=4, D=64, seed=0, drift=0.05, dividers=[1, 2, 2, 1]),
+    4: dict(B=2, S=1200, H=4, D=128, seed=1, drift=0.05, dividers=[1, 4, 4, 2, 2, 2, 1]),
+    8: dict(B=1, S=2048, H=8, D=64, seed=2, drift=0.05, dividers=[1, 1, 1, 8, 8, 8, 8, 4, 4, 2, 2, 1, 1]),
+}
+
+
+def parity_miniature(world, rank, group, device):
+    """Before anything is timed: the attention path on this job's real process group (NCCL) against the
+    CPU oracle on a small seeded case -- ring with cached reuse over a schedule through every divider,
+    and the Ulysses exchange.  The oracle is the checker only.  Returns this rank's worst errors."""
+    from oracle import ring_oracle as O
+    from ditango_b200 import ops
+    from ditango_b200.baseline.ulysses import ulysses_attention
+    from ditango_b200.core import redundancy_map as rmod
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.config import get_config
+    from ditango_b200.utils import update_timestep
+    case = PARITY_CASES.get(world)
+    if case is None:
+        return None
+    cfg = get_config()
+    keep = (cfg.num_layers, cfg.num_inference_steps)
+    div = case["dividers"]
+    cfg.num_layers, cfg.num_inference_steps = 1, len(div)
+    rmod.destroy_redundancy_map()
+    rm = rmod.init_redundancy_map(cfg, world_size=world)
+    for t, d in enumerate(div):
+        rm.divider_map[t, 0] = d
+    layer = proAttention(0, group)
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"], dtype=torch.bfloat16)
+    ref, states = O.run_ring_group(world, div, data)
+    lo, hi = rank * S // world, (rank + 1) * S // world
+    worst = dict(max_abs=0.0, mean_abs=0.0, lse_max=0.0, ulysses_max_abs=0.0)
+    for t in range(len(div)):
+        update_timestep(t)
+        out = layer.attn(*(x[:, lo:hi].contiguous().to(device) for x in data[t])).float().cpu()
+        e = (out - ref[t][rank]).abs()
+        worst["max_abs"] = max(worst["max_abs"], e.max().item())
+        worst["mean_abs"] = max(worst["mean_abs"], e.mean().item())
+    got_lse = layer.last_lse.float().cpu().transpose(-1, -2).unsqueeze(-1)
+    worst["lse_max"] = (got_lse - states[rank].last_lse).abs().max().item()
+    q, k, v = data[0]
+    full, _ = O.partial_attention(q, k, v, out_dtype=torch.float32)
+    uly = ulysses_attention(*(x[:, lo:hi].contiguous().to(device) for x in (q, k, v)), group=group).float().cpu()
+    worst["ulysses_max_abs"] = (uly - full[:, lo:hi]).abs().max().item()
+    worst["status"] = float(ops.read_status())
+    del layer
+    rmod.destroy_redundancy_map()
+    cfg.num_layers, cfg.num_inference_steps = keep
+    update_timestep(0)
+    return worst
+
+
 def run_ours(args):
     import torch.distributed as dist
     from ditango_b200 import _capi, ops
     from ditango_b200.core import parallel_state as ps
-    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.attention import proAttention, release_receive_slots
     from ditango_b200.core.config import init_config
     from ditango_b200.core.group_coordinate import SingleRankGroup
     from ditango_b200.core.redundancy_map import init_redundancy_map
@@ -193,6 +250,19 @@ def run_ours(args):
         group = ps.get_isp_group()
     else:
         group = SingleRankGroup(device)
+    parity = None
+    if world > 1 and not args.no_parity:
+        mine = parity_miniature(world, rank, group, device)
+        if mine is not None:
+            keys = ["max_abs", "mean_abs", "lse_max", "ulysses_max_abs", "status"]
+            tp = torch.tensor([mine[k] for k in keys], device=device, dtype=torch.float64)
+            dist.all_reduce(tp, op=dist.ReduceOp.MAX)
+            parity = {k: float(f"{x:.3e}") for k, x in zip(keys, tp.tolist())}
+            parity["case"] = ("proAttention.attn on this job's NCCL group vs the CPU oracle, max over ranks and steps: "
+                              + json.dumps(PARITY_CASES[world]))
+            parity["within_tolerance"] = bool(parity["max_abs"] <= 2e-2 and parity["mean_abs"] <= 1e-3
+                                              and parity["lse_max"] <= 1e-3 and parity["ulysses_max_abs"] <= 2e-2
+                                              and parity["status"] == 0)
     rm = init_redundancy_map(cfg, world_size=world)
     reuse_cells = 0
     if args.mode == "ditango" and world > 1 and args.schedule == "pairs":
@@ -246,6 +316,7 @@ def run_ours(args):
         L.measure_comm = world > 1
         L.exposed_comm_ms()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rx_before = sum(L.stats["bytes_received"] for L in layers)
     barrier()
     ev0.record()
     for t in range(args.warmup, total_steps):
@@ -253,6 +324,10 @@ def run_ours(args):
     ev1.record()
     barrier()
     elapsed_ms = ev0.elapsed_time(ev1)
+    rx_timed = sum(L.stats["bytes_received"] for L in layers) - rx_before
+    if args.mode == "ulysses" and world > 1:
+        # q, k, v out and the result back: (N-1)/N of each leaves the rank per layer call
+        rx_timed = int(4 * (world - 1) / world * B * S_loc * H * D * 2) * w["layers"] * args.steps
     clocks = sampler.stop() if rank == 0 else None
     launches = ops.LaunchLog.count
     flash_ms = [a.elapsed_time(b) for a, b, _ in ops.LaunchLog.events]
@@ -266,21 +341,29 @@ def run_ours(args):
         raise SystemExit(f"kernel status {status} in the timed region")
 
     # ---------------------------------------------------------------- end-to-end (host buffers)
+    # What a caller with host-resident activations pays per layer call: q and K||V (one buffer, two copies
+    # instead of three) go pinned host -> device, the result comes back as bf16 -- the dtype the
+    # reference's callers cast to at once (executor/cogvideox/attention_processor.py:80) -- with the cast
+    # fused into the last kernel of the call (proAttention.output_dtype).
     e2e_steps = args.steps
     q, k, v = prepared[0]
-    host_in = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for x in (q, k, v)]
-    for h, x in zip(host_in, (q, k, v)):
-        h.copy_(x)
-    out_dtype = torch.bfloat16 if args.mode == "ulysses" else torch.float32
-    host_out = torch.empty(q.shape, dtype=out_dtype).pin_memory()
+    host_q = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    host_kv = torch.empty((2,) + tuple(k.shape), dtype=k.dtype).pin_memory()
+    host_q.copy_(q)
+    host_kv[0].copy_(k)
+    host_kv[1].copy_(v)
+    host_out = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
     # Two device input slots: the copies of layer l+1 run on a copy stream while layer l computes;
     # results leave on a second copy stream.  Every byte still crosses PCIe inside the timed region.
-    dev_in = [[torch.empty_like(x) for x in (q, k, v)] for _ in range(2)]
-    h2d = sum(h.numel() * h.element_size() for h in host_in) * w["layers"]
+    dev_q = [torch.empty_like(q) for _ in range(2)]
+    dev_kv = [torch.empty((2,) + tuple(k.shape), dtype=k.dtype, device=device) for _ in range(2)]
+    h2d = (host_q.numel() * host_q.element_size() + host_kv.numel() * host_kv.element_size()) * w["layers"]
     d2h = host_out.numel() * host_out.element_size() * w["layers"]
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_free = [torch.cuda.Event() for _ in range(2)]
+    for L in layers:
+        L.output_dtype = torch.bfloat16
 
     def e2e_step(t):
         update_timestep((t0 + t) % w["steps"])
@@ -290,8 +373,8 @@ def run_ours(args):
             slot = l & 1
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_free[slot])
-                for d, h in zip(dev_in[slot], host_in):
-                    d.copy_(h, non_blocking=True)
+                dev_q[slot].copy_(host_q, non_blocking=True)
+                dev_kv[slot].copy_(host_kv, non_blocking=True)
                 ev_in[slot].record(s_in)
         for slot in range(2):
             ev_free[slot].record(main)
@@ -301,7 +384,8 @@ def run_ours(args):
             if l + 1 < w["layers"]:
                 fetch(l + 1)
             main.wait_event(ev_in[slot])
-            o = ulysses_attention(*dev_in[slot], group=group) if args.mode == "ulysses" else layers[l].attn(*dev_in[slot])
+            qkv = (dev_q[slot], dev_kv[slot][0], dev_kv[slot][1])
+            o = ulysses_attention(*qkv, group=group) if args.mode == "ulysses" else layers[l].attn(*qkv)
             ev_free[slot].record(main)
             done = torch.cuda.Event()
             done.record(main)
@@ -323,15 +407,80 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     e2e_flops = sum(f for _, _, f in ops.LaunchLog.events)
     ops.LaunchLog.reset(with_events=False)
+    for L in layers:
+        L.output_dtype = torch.float32
+
+    # Host-side ceiling of that region: all ranks move the same bytes host <-> device at once with no
+    # kernels in between (both directions concurrently, as the e2e region does).
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(2, min(w["layers"], 8))
+    c0.record()
+    for _ in range(reps):
+        with torch.cuda.stream(s_in):
+            dev_q[0].copy_(host_q, non_blocking=True)
+            dev_kv[0].copy_(host_kv, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            host_out.copy_(dev_q[1], non_blocking=True)
+    torch.cuda.current_stream().wait_stream(s_in)
+    torch.cuda.current_stream().wait_stream(s_out)
+    c1.record()
+    barrier()
+    copy_ms = c0.elapsed_time(c1) / reps * w["layers"]       # per step, copies only
+
+    # ---------------------------------------------------------------- plain ring, same steps
+    # The comparison behind "exposed communication vs plain ring attention": the same code with an all-ones
+    # divider map (every step a full refresh, every chunk fetched and attended; core/config.py:58-59 of the
+    # reference makes that the behaviour of every mode but use-ditango).  Fresh layer objects, nothing cached.
+    plain = None
+    if world > 1 and args.mode == "ditango" and not args.no_plain_ring:
+        stats_keep = [dict(L.stats) for L in layers]
+        del layers
+        release_receive_slots()
+        torch.cuda.empty_cache()
+        rm.set_pair_map(None)
+        rm.divider_map = torch.ones(w["steps"], w["layers"], dtype=torch.long)
+        ring_layers = [proAttention(l, group) for l in range(w["layers"])]
+
+        def ring_step(t, qkv):
+            update_timestep(t % w["steps"])
+            for L in ring_layers:
+                L.attn(*qkv)
+        for t in range(min(args.warmup, 2)):
+            ring_step(t, prepared[t % n_prepared])
+        for L in ring_layers:
+            L.measure_comm = True
+            L.exposed_comm_ms()
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for t in range(args.steps):
+            ring_step(2 + t, prepared[t % n_prepared])
+        r1.record()
+        barrier()
+        plain = [r0.elapsed_time(r1), sum(L.exposed_comm_ms() for L in ring_layers)]
+        layers = ring_layers
+        if ops.read_status() != 0:
+            raise SystemExit("kernel status non-zero in the plain-ring pass")
+    else:
+        stats_keep = [dict(L.stats) for L in layers]
 
     # ---------------------------------------------------------------- reduce over ranks
-    stats = torch.tensor([elapsed_ms, e2e_ms, exposed_ms], device=device, dtype=torch.float64)
+    stats = torch.tensor([elapsed_ms, e2e_ms, exposed_ms, copy_ms] + (plain if plain is not None else [0.0, 0.0]),
+                         device=device, dtype=torch.float64)
     sums = torch.tensor([sum(flash_flops), e2e_flops, sum(flash_ms), float(len(flash_ms)), float(launches)],
+                        device=device, dtype=torch.float64)
+    # whole-path roofline of this rank's timed steps: the slower of its MMA work at the measured bf16 peak
+    # and its received KV bytes at the measured peer-copy bandwidth (770 GB/s per direction on this pool)
+    pk = measured_peaks()
+    roof = torch.tensor([max(sum(flash_flops) / (pk["tensor"] * 1e12), rx_timed / 770e9) * 1e3,
+                         sum(flash_flops) / (pk["tensor"] * 1e12) * 1e3, rx_timed / 770e9 * 1e3],
                         device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    elapsed_ms, e2e_ms, exposed_ms = stats.tolist()
+        dist.all_reduce(roof, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, exposed_ms, copy_ms, plain_ms, plain_exposed_ms = stats.tolist()
     tot_flops, tot_e2e_flops, tot_flash_ms, n_flash, tot_launches = sums.tolist()
 
     cpu = None
@@ -364,11 +513,29 @@ def run_ours(args):
                          "traffic": round(flash_dram_traffic(B, S_loc, H, D)),
                          "traffic_kind": "bytes per launch, scaled by tensor size from the ncu capture of a smaller chunk pair"},
             "clocks": clocks,
+            "path_roofline": {"t_roof_ms_per_step": round(roof[0].item() / args.steps, 3),
+                              "mma_ms_per_step": round(roof[1].item() / args.steps, 3),
+                              "kv_transfer_ms_per_step": round(roof[2].item() / args.steps, 3),
+                              "frac": round(roof[0].item() / elapsed_ms, 4),
+                              "formula": "max over ranks of max(executed FLOPs / sustained bf16 peak, KV bytes received / 770 GB/s)"},
             "e2e": {"value": round(tot_e2e_flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                     "ms_per_step": round(e2e_ms / e2e_steps, 3),
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                    "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
+                    "result_dtype": "bf16 (cast fused into the last kernel of each call)",
+                    "host_copy_ms_per_step": round(copy_ms, 3),
+                    "host_copy_gbs": round((h2d + d2h) * world / (copy_ms * 1e-3) / 1e9, 1),
+                    "host_copy_kind": "the region's copies alone, all ranks at once, no kernels: the floor the "
+                                      "host side sets for an e2e step"},
             "gpu_launches": int(tot_launches),
         }
+        if parity is not None:
+            line["parity"] = parity
+        if plain_ms > 0:
+            line["plain_ring"] = {"ms_per_step": round(plain_ms / args.steps, 3),
+                                  "exposed_comm_ms_per_step": round(plain_exposed_ms / args.steps, 3),
+                                  "kind": "same code, all-ones divider map (every chunk fetched and attended every step)"}
+            line["exposed_comm_ratio_plain_over_ditango"] = round(plain_exposed_ms / max(exposed_ms, 1e-6), 2)
+            line["step_time_ratio_plain_over_ditango"] = round(plain_ms / elapsed_ms, 3)
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -407,30 +574,87 @@ def cpu_baseline(w, world, sample_seq=None, steps=1, min_seconds=0.0):
                       f"full workload is S={w['S']} x {w['layers']} layers per step"}
 
 
+def reference_sample_schedule(world, p, steps=8, seed=0):
+    """Dividers of one layer for a `steps`-step sample: Bernoulli(p) reuse drawn like the GPU arm's
+    schedule, legalised, screened, with the first step a full refresh."""
+    from ditango_b200.core.config import init_config
+    from ditango_b200.core import redundancy_map as rmod
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = 1, steps
+    rmod.destroy_redundancy_map()
+    rm = rmod.init_redundancy_map(cfg, world_size=world)
+    div = draw_dividers(steps, 1, world, p, seed=seed)
+    for t in range(1, steps):          # a divider may only fall, or restart from 1 (core/redundancy_map.py:281-326)
+        if div[t - 1, 0] != 1 and div[t, 0] > div[t - 1, 0]:
+            div[t, 0] = 1
+    rm.divider_map = torch.from_numpy(div)
+    rm.screen_self_sends()
+    out = [int(x) for x in rm.get_map()[:, 0].tolist()]
+    rmod.destroy_redundancy_map()
+    return out
+
+
+def executed_reference(w, world, sample_seq, mode):
+    """The reference's own proAttention.attn (the copy under oracle/_ref, made by oracle/make_ref.py) on
+    `world` gloo ranks of this host, one layer, a few steps of the workload's schedule at a reduced
+    sequence length.  None when the copy is absent or the group has one rank (the reference has no
+    attention group then)."""
+    from oracle import ref_runner as R
+    if world < 2 or not R.available():
+        return None
+    B, H, D = w["B"], w["H"], w["D"]
+    s_loc = max(256, (sample_seq or 4096) // world)
+    div = reference_sample_schedule(world, w["p"]) if mode == "ditango" else [1] * 4
+    case = dict(B=B, S=s_loc * world, H=H, D=D, dividers=div, rms=w["rms"], bf16=True)
+    r = R.time_reference(world, case)
+    return {"value": round(r["flops"] / r["seconds"] / 1e12, 4), "unit": "TFLOP/s", "cores": r["cores"], "kind": "reference",
+            "seconds": round(r["seconds"], 2),
+            "sample": f"the reference's proAttention.attn, unmodified, on {world} gloo ranks of this host (its GPU-only "
+                      f"flash_attn call replaced by fp32 softmax arithmetic on the host cores): 1 layer x {len(div)} steps, "
+                      f"dividers {div}, B={B} H={H} D={D} S={s_loc * world}; full workload is S={w['S']} x {w['layers']} layers per step"}
+
+
+def config1_reference():
+    """Benchmark configuration 1 at full size on the executed reference: 2 gloo ranks, B1 H4 S1024 D64 fp32,
+    4 steps, dividers 1,2,2,1 (one Bernoulli(0.5) draw with step 0 a full refresh)."""
+    from oracle import ref_runner as R
+    if not R.available():
+        return None
+    r = R.time_reference(2, dict(B=1, S=1024, H=4, D=64, dividers=[1, 2, 2, 1], bf16=False, seed=0), port=29890)
+    return {"ms_per_step": round(r["seconds"] / r["steps"] * 1e3, 2), "tflops": round(r["flops"] / r["seconds"] / 1e12, 4),
+            "ranks": 2, "cores": r["cores"], "kind": "reference",
+            "config": "B=1 H=4 S=1024 D=64 fp32, 4 steps, dividers [1,2,2,1], one layer"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     w = dict(WORKLOADS[args.workload])
     t_all = []
-    cpu = None
     for i in range(args.warmup + args.steps):
-        cpu = cpu_baseline(w, args.gpus, sample_seq=args.cpu_seq, steps=1, min_seconds=4.0)
+        cpu = executed_reference(w, args.gpus, args.cpu_seq, args.mode)
+        if cpu is None:
+            cpu = cpu_baseline(w, args.gpus, sample_seq=args.cpu_seq, steps=1, min_seconds=4.0)
         if i >= args.warmup:
             t_all.append(cpu)
     value = statistics.mean(c["value"] for c in t_all)
-    secs = statistics.mean(c["seconds"] for c in t_all)
     cpu = dict(t_all[-1], value=round(value, 4))
+    c1 = config1_reference()
+    if c1 is not None:
+        cpu["config1"] = c1
     B, H, D, S = w["B"], w["H"], w["D"], w["S"]
     full_step_flops = 4.0 * B * H * float(S) * S * D * w["layers"]
     line = {
         "impl": "reference", "metric": "attention TFLOP/s (executed FLOPs, whole job) and ms per denoising step",
         "value": round(value, 4), "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(full_step_flops / (value * 1e12) * 1e3, 1), "ms_per_step_kind": "extrapolated from the sample",
+        "ms_per_step": round(full_step_flops / (value * 1e12) * 1e3, 1),
+        "ms_per_step_kind": "extrapolated from the sample's FLOP rate to one full-attention step of the workload",
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 inputs, fp32 arithmetic",
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: {w['desc']}; B={B} H={H} D={D} S={S}, {w['layers']} layers/step",
-                   "mode": "ring", "global_batch": B, "seq_len": S, "layers_per_step": w["layers"]},
+                   "mode": args.mode if cpu["kind"] == "reference" else "ring", "global_batch": B, "seq_len": S,
+                   "layers_per_step": w["layers"]},
         "cpu_baseline": cpu,
         "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -549,8 +773,9 @@ def run_micro(args):
         work, unit, peak, bound = 4.0 * B * H * S * S * D, "TFLOP/s", peaks["tensor_burst"], "tensor"
     elif args.micro == "merge":
         n = args.states
-        st = [(rnd(B, S, H, D), rnd(B, H, S), ops.LSE_BHS) for _ in range(n)]
-        fn = lambda: ops.merge_states(st, out=st[0][0], lse_out=st[0][1], lse_out_layout=ops.LSE_BHS)
+        lay = ops.LSE_BSH if args.lse_layout == "bsh" else ops.LSE_BHS
+        st = [(rnd(B, S, H, D), rnd(B, S, H) if lay == ops.LSE_BSH else rnd(B, H, S), lay) for _ in range(n)]
+        fn = lambda: ops.merge_states(st, out=st[0][0], lse_out=st[0][1], lse_out_layout=lay)
         work, unit, peak, bound = float((n + 1) * B * S * H * (D * 4 + 4)), "GB/s", peaks["hbm"], "hbm"
     else:
         N = 8
@@ -573,7 +798,8 @@ def run_micro(args):
     ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     rate = work / (ms * 1e-3) / (1e12 if bound == "tensor" else 1e9)
     print(json.dumps({"micro": args.micro, "workload": args.workload, "shape": dict(B=B, S=S, H=H, D=D),
-                      "states": args.states if args.micro == "merge" else None, "ms": round(ms, 4),
+                      "states": args.states if args.micro == "merge" else None,
+                      "lse_layout": args.lse_layout if args.micro == "merge" else None, "ms": round(ms, 4),
                       "achieved": round(rate, 1), "unit": unit, "peak": peak, "frac": round(rate / peak, 4),
                       "status": ops.read_status()}), flush=True)
 
@@ -596,9 +822,13 @@ def main():
                     help="transport batches per call: one per hop, or batches of 1, 2, 4, ... hops")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity miniature that runs before the warm-up at N > 1")
+    ap.add_argument("--no-plain-ring", action="store_true", help="skip the plain-ring comparison pass at N > 1")
     ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy"], help="time one kernel and exit")
     ap.add_argument("--shard", type=int, default=8, help="--micro: tokens = S / shard")
     ap.add_argument("--states", type=int, default=4, help="--micro merge: number of states")
+    ap.add_argument("--lse-layout", default="bsh", choices=["bsh", "bhs"],
+                    help="--micro merge: lse as [B,S,H] (what the attention path keeps internally) or [B,H,S]")
     args = ap.parse_args()
     if args.micro:
         return run_micro(args)

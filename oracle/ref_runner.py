@@ -1,0 +1,107 @@
+"""Times the REFERENCE's own per-layer attention object (the copy made by oracle/make_ref.py) on CPU/gloo
+ranks of this host.  BENCHMARK INFRASTRUCTURE ONLY: the product never imports this.
+
+The reference's hot path runs unmodified (core/attention.py:73-237 of the reference: proAttention.attn);
+only what cannot exist on a CPU box is replaced, the same four shims tests/golden/make_golden.py uses:
+matplotlib -> stub modules; torch.cuda.get_device_properties / memory_allocated (core/cache.py:22,123) ->
+fakes; flash_attn_func (a GPU-only third-party wheel) -> fp32 softmax(QK^T/sqrt(D))V + logsumexp on the
+host cores; the copy exposed as package `ditango`.
+"""
+import math
+import os
+import sys
+import tempfile
+import time
+import types
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REFPKG = os.path.join(HERE, "_ref")
+_FLOPS = [0.0]
+
+
+def available() -> bool:
+    return os.path.exists(os.path.join(REFPKG, "ditango", "core", "attention.py"))
+
+
+def _cpu_flash(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, return_attn_probs=False, **kw):
+    scale = softmax_scale or 1.0 / math.sqrt(q.shape[-1])
+    _FLOPS[0] += 4.0 * q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1] * q.shape[3]
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    lse = torch.logsumexp(s, dim=-1)
+    o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.float()).to(q.dtype)
+    return (o, lse, None) if return_attn_probs else o
+
+
+def _worker(rank, world, case, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
+                      RANK=str(rank), LOCAL_RANK=str(rank))
+    os.chdir(tempfile.mkdtemp(prefix="ditango_ref_"))          # init_config() makes ./result/<tag>_<ts>
+    m, mpp = types.ModuleType("matplotlib"), types.ModuleType("matplotlib.pyplot")
+    m.pyplot = mpp
+    sys.modules["matplotlib"], sys.modules["matplotlib.pyplot"] = m, mpp
+    sys.path.insert(0, REFPKG)
+
+    class _Props:
+        total_memory = 180 * 2 ** 30
+    torch.cuda.get_device_properties = lambda i: _Props()
+    torch.cuda.memory_allocated = lambda *a, **k: 0
+    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
+
+    import ditango.core.attention as A
+    A.flash_attn_func = _cpu_flash
+    from ditango.core import parallel_state as ps
+    from ditango.core.config import init_config
+    from ditango.core.redundancy_map import get_redundancy_map, init_redundancy_map
+    from ditango.utils import update_timestep
+
+    div = case["dividers"]
+    cfg = init_config(None)
+    cfg.num_layers, cfg.num_inference_steps = 1, len(div)
+    ps.init_distributed_environment(world_size=world, rank=rank, local_rank=rank, backend="gloo")
+    c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
+    ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
+    init_redundancy_map(cfg)
+    rm = get_redundancy_map()
+    for t, d in enumerate(div):
+        rm.divider_map[t, 0] = d
+    layer = A.proAttention(0, ps.get_isp_group())
+    B, S, H, D = case["B"], case["S"], case["H"], case["D"]
+    g = torch.Generator().manual_seed(case.get("seed", 0) * 1000 + rank)
+    dt = torch.bfloat16 if case.get("bf16", True) else torch.float32
+    lo = S // world
+    q, k, v = (torch.randn(B, lo, H, D, generator=g) for _ in range(3))
+    seconds = 0.0
+    for t in range(len(div)):
+        if t > 0:
+            q, k, v = (x + case.get("drift", 0.05) * torch.randn(x.shape, generator=g) for x in (q, k, v))
+        qq, kk = q, k
+        if case.get("rms"):
+            qq = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + 1e-6)
+            kk = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + 1e-6)
+        args = (qq.to(dt), kk.to(dt), v.to(dt))
+        update_timestep(t)
+        dist.barrier()
+        t0 = time.perf_counter()
+        layer.attn(*args)
+        dist.barrier()
+        seconds += time.perf_counter() - t0
+    ret[rank] = (seconds, _FLOPS[0])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def time_reference(world, case, port=29790):
+    """Runs the reference's proAttention.attn for len(case['dividers']) steps of one layer on `world` gloo
+    ranks (world >= 2: the reference has no attention group at one rank).  Returns
+    dict(seconds, flops, steps, cores)."""
+    assert world >= 2 and available()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, case, port + int(time.time()) % 97, ret), nprocs=world, join=True)
+    secs = max(ret[r][0] for r in range(world))
+    flops = sum(ret[r][1] for r in range(world))
+    return dict(seconds=secs, flops=flops, steps=len(case["dividers"]), cores=os.cpu_count() or 1)

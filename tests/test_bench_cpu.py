@@ -22,6 +22,24 @@ def test_reference_arm_prints_one_json_line():
         assert key in d
 
 
+def test_reference_arm_runs_the_executed_reference_when_its_copy_is_present():
+    """With oracle/_ref/ (made by oracle/make_ref.py from a checkout of the reference) the arm times the
+    reference's own proAttention.attn on gloo ranks and adds benchmark configuration 1 at full size."""
+    import pytest
+    from oracle import ref_runner
+    if not ref_runner.available():
+        pytest.skip("no copy of the reference under oracle/_ref")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                          "--warmup", "0", "--cpu-seq", "512", "--workload", "cogvideox"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT,
+                         env={k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE")})
+    assert out.returncode == 0, out.stderr[-2000:]
+    d = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][0])
+    assert d["cpu_baseline"]["kind"] == "reference" and d["value"] > 0
+    c1 = d["cpu_baseline"]["config1"]
+    assert c1["ranks"] == 2 and c1["ms_per_step"] > 0
+
+
 def test_other_ranks_of_the_reference_arm_stay_silent():
     env = dict(os.environ, RANK="1", WORLD_SIZE="2")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
