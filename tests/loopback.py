@@ -183,19 +183,25 @@ class LoopbackGroup:
         self.fabric.barrier()
 
 
-def run_ranks(world: int, body: Callable[[int, LoopbackGroup, LoopbackFabric], object], timeout_s: float = 120.0):
+def run_ranks(world: int, body: Callable[[int, LoopbackGroup, LoopbackFabric], object], timeout_s: float = 120.0,
+              prepare: Optional[Callable[[int, LoopbackGroup], object]] = None):
     """Run body(rank, group, fabric) on `world` threads; returns the list of results, or raises the
-    first exception any rank raised."""
+    first exception any rank raised.  `prepare(rank, group)`, if given, runs for every rank in the calling
+    thread before the threads start (anything that draws from the process-wide random generator belongs
+    there); its result is left in group.context."""
     fabric = LoopbackFabric(world, timeout_s)
     results = [None] * world
     errors = []
     device = torch.cuda.current_device() if torch.cuda.is_available() else None
+    groups = [fabric.group(r) for r in range(world)]
+    for r, g in enumerate(groups):
+        g.context = prepare(r, g) if prepare is not None else None
 
     def target(r):
         try:
             if device is not None:
                 torch.cuda.set_device(device)
-            results[r] = body(r, fabric.group(r), fabric)
+            results[r] = body(r, groups[r], fabric)
         except BaseException as e:  # noqa: BLE001 - surfaced to the caller below
             errors.append((r, e))
             fabric.abort(e)
