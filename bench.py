@@ -248,6 +248,9 @@ def run_ours(args):
         c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
         ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
         group = ps.get_isp_group()
+        if args.transport == "peer":
+            from ditango_b200.core.peer_transport import PeerCopyGroup
+            group = PeerCopyGroup(group)
     else:
         group = SingleRankGroup(device)
     parity = None
@@ -502,7 +505,8 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (Q,K,V of one layer call exceed 126 MB)",
                        "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0,
                        "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none",
-                       "hop_grouping": args.hop_grouping if (args.mode != "ulysses" and world > 1) else "none"},
+                       "hop_grouping": args.hop_grouping if (args.mode != "ulysses" and world > 1) else "none",
+                       "transport": args.transport if (args.mode != "ulysses" and world > 1) else "none"},
             "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
             "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
             "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
@@ -692,6 +696,9 @@ def run_dit(args):
         c, u, i = ps.generate_parallel_groups(world, do_cfg_guidance=False, sparse_type="full")
         ps.init_model_parallel(cfg_group_ranks=c, usp_group_ranks=u, iosp_dict=i)
         group = ps.get_isp_group()
+        if args.transport == "peer" and args.mode != "ulysses":
+            from ditango_b200.core.peer_transport import PeerCopyGroup
+            group = PeerCopyGroup(group)
     else:
         group = SingleRankGroup(device)
     rm = init_redundancy_map(cfg, world_size=world)
@@ -742,7 +749,8 @@ def run_dit(args):
             "unit": "ms/step", "higher_is_better": False, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "dtype": "bf16", "data": "synthetic", "scaling": "strong",
             "config": {"workload": f"cogvideox-dit: {dcfg.num_layers} layers, hidden {dcfg.dim}, {dcfg.num_heads}x{dcfg.head_dim} heads, "
-                                   f"{dcfg.video_tokens}+{dcfg.text_len} tokens, CFG batch 2, mode={args.mode}", "mode": args.mode},
+                                   f"{dcfg.video_tokens}+{dcfg.text_len} tokens, CFG batch 2, mode={args.mode}", "mode": args.mode,
+                       "transport": args.transport if args.mode != "ulysses" else "none"},
             "exposed_comm_ms_per_step": round(exposed / args.steps, 3),
             "attention_kernel_ms_per_step": round(flash_ms / args.steps, 3),
             "attention_kernel_tflops": round(flash_flops / max(flash_ms, 1e-9) / 1e9, 1),
@@ -820,6 +828,8 @@ def main():
                     help="ditango mode: stride schedule (what the reference can express) or a per-pair reuse map")
     ap.add_argument("--hop-grouping", default="single", choices=["single", "doubling"],
                     help="transport batches per call: one per hop, or batches of 1, 2, 4, ... hops")
+    ap.add_argument("--transport", default="nccl", choices=["nccl", "peer"],
+                    help="KV hops by NCCL send/receive, or by copy-engine copies into IPC-mapped buffers of the consumer")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity miniature that runs before the warm-up at N > 1")

@@ -19,6 +19,7 @@ MERGE_MAX_STATES = 16
 EXPORTS = (
     "dtb_version", "dtb_last_error", "dtb_device_supported", "dtb_read_status",
     "dtb_peek_status_async", "dtb_post_status",
+    "dtb_ipc_export_mem", "dtb_ipc_open_mem", "dtb_ipc_close_mem", "dtb_peer_copy_async",
     "dtb_flash_fwd", "dtb_merge_states", "dtb_copy_chunks",
     "dtb_drift_scratch_bytes", "dtb_drift_accumulate",
     "dtb_drift_noalloc_max_elements", "dtb_drift_accumulate_noalloc",
@@ -52,6 +53,14 @@ def load():
     lib.dtb_peek_status_async.argtypes = [c_void_p, c_void_p]
     lib.dtb_post_status.restype = c_int
     lib.dtb_post_status.argtypes = [c_int, c_void_p]
+    lib.dtb_ipc_export_mem.restype = c_int
+    lib.dtb_ipc_export_mem.argtypes = [c_void_p, c_void_p, POINTER(c_int64)]
+    lib.dtb_ipc_open_mem.restype = c_int
+    lib.dtb_ipc_open_mem.argtypes = [c_void_p, POINTER(c_void_p)]
+    lib.dtb_ipc_close_mem.restype = c_int
+    lib.dtb_ipc_close_mem.argtypes = [c_void_p]
+    lib.dtb_peer_copy_async.restype = c_int
+    lib.dtb_peer_copy_async.argtypes = [c_void_p, c_void_p, c_int64, c_void_p]
     lib.dtb_flash_fwd.restype = c_int
     lib.dtb_flash_fwd.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -141,10 +141,12 @@ class proAttention:
         src = plan.recv_from(me, hop)
         recv = None
         for dst in plan.send_to(me, hop):
-            for t in payload:
-                self.group.p2p_isend(t, dst=dst)
+            for i, t in enumerate(payload):
+                self.group.p2p_isend(t, dst=dst, slot=("kv", hop, i))
         if src is not None:
-            recv = tuple(self.group.p2p_irecv(src=src, out=_slot(self.group, f"kv{i}", hop, t)) for i, t in enumerate(payload))
+            own_buffers = hasattr(self.group, "p2p_prepare")     # the transport lands the data in buffers of its own
+            recv = tuple(self.group.p2p_irecv(src=src, out=None if own_buffers else _slot(self.group, f"kv{i}", hop, t),
+                                              slot=("kv", hop, i)) for i, t in enumerate(payload))
             self.stats["chunks_received"] += 1
             self.stats["bytes_received"] += sum(t.numel() * t.element_size() for t in payload)
         return recv
@@ -157,6 +159,9 @@ class proAttention:
         process group run one after another, each moving one chunk per rank at the rate of one peer pair.
         "doubling": batches of 1, 2, 4, ... hops -- the first chunk still arrives as early as possible,
         later batches pull from several peers at once.  Every rank of the group must use the same setting."""
+        prepare = getattr(self.group, "p2p_prepare", None)
+        if prepare is not None:              # transports that keep their own receive buffers (peer_transport.py)
+            prepare("kv", payload, self.isp_size)
         posted, size, hop = [], 1, 0
         while hop < n_hops:
             end = min(n_hops, hop + size)

@@ -108,12 +108,14 @@ class GroupCoordinator:
         dist.barrier(group=self.cpu_group)
 
     # ------------------------------------------------------------------ batched point-to-point
-    def p2p_isend(self, tensor: torch.Tensor, dst: Optional[int] = None):
+    def p2p_isend(self, tensor: torch.Tensor, dst: Optional[int] = None, slot=None):
+        """`slot` names the receive buffer on the consumer (tag, hop, payload index); NCCL matches sends and
+        receives by order and ignores it."""
         if dst is None:
             dst = (self.rank_in_group + 1) % self.world_size
         self.p2p_ops.append(dist.P2POp(dist.isend, tensor, self.ranks[dst], self.device_group))
 
-    def p2p_irecv(self, size=None, dtype=None, src: Optional[int] = None, out: Optional[torch.Tensor] = None):
+    def p2p_irecv(self, size=None, dtype=None, src: Optional[int] = None, out: Optional[torch.Tensor] = None, slot=None):
         """Queue a receive from group rank `src`.  `out` receives in place (persistent slot); without
         it a tensor of `size`/`dtype` is allocated, as the reference does on every hop."""
         if src is None:

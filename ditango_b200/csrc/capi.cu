@@ -175,6 +175,55 @@ DTB_API int dtb_post_status(int code, void* stream) {
   return DTB_OK;
 }
 
+DTB_API int dtb_ipc_export_mem(const void* dev_ptr, void* handle64, int64_t* offset) {
+  if (!dev_ptr || !handle64 || !offset) return fail(DTB_ERR_ARG, "dtb_ipc_export_mem: null argument");
+  static PFN_cuMemGetAddressRange_v3020 get_range = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      get_range = reinterpret_cast<PFN_cuMemGetAddressRange_v3020>(fn);
+  });
+  if (get_range == nullptr) return fail(DTB_ERR_CUDA, "dtb_ipc_export_mem: cuMemGetAddressRange not available");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  CUresult r = get_range(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr));
+  if (r != CUDA_SUCCESS) return fail(DTB_ERR_CUDA, "dtb_ipc_export_mem: address range query failed with CUresult %d", static_cast<int>(r));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+  static_assert(sizeof(h) == 64, "handle size");
+  memcpy(handle64, &h, sizeof(h));
+  *offset = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+  return DTB_OK;
+}
+
+DTB_API int dtb_ipc_open_mem(const void* handle64, void** base_ptr) {
+  if (!handle64 || !base_ptr) return fail(DTB_ERR_ARG, "dtb_ipc_open_mem: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(base_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
+DTB_API int dtb_ipc_close_mem(void* base_ptr) {
+  if (!base_ptr) return DTB_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(base_ptr);
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "cudaIpcCloseMemHandle failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
+DTB_API int dtb_peer_copy_async(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (bytes < 0 || (bytes > 0 && (!dst || !src))) return fail(DTB_ERR_ARG, "dtb_peer_copy_async: bad argument");
+  if (bytes == 0) return DTB_OK;
+  cudaError_t e = cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDefault, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "peer copy failed: %s", cudaGetErrorString(e));
+  return DTB_OK;
+}
+
 DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
                   int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
                   void* out, int out_dtype, int64_t out_tok_stride,

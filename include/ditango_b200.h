@@ -77,6 +77,28 @@ DTB_API int dtb_peek_status_async(int* host_word, void* stream);
 DTB_API int dtb_post_status(int code, void* stream);
 
 /*
+ * Copy-engine KV transport between the GPUs of one node.  Replaces the NCCL send / receive pairs behind
+ * GroupCoordinator.p2p_isend / p2p_irecv / p2p_commit (core/group_coordinate.py:643-668) as used by
+ * async_ring_p2p_commit (core/attention.py:37-62): the owner of a KV chunk writes it straight into a
+ * receive buffer of the consumer with one asynchronous device-to-device copy, which a copy engine
+ * executes -- no SM is taken from the attention kernel.
+ *
+ *  dtb_ipc_export_mem   consumer side: the 64-byte CUDA IPC handle of the allocation that contains
+ *                       dev_ptr, and dev_ptr's byte offset inside it (the caller ships both to the peer).
+ *  dtb_ipc_open_mem     owner side: maps the peer's allocation into this process for the CURRENT device
+ *                       (peer access is enabled on demand) and returns its base address; add the offset.
+ *                       Map a handle once and keep it; close it with dtb_ipc_close_mem at shutdown.
+ *  dtb_peer_copy_async  one asynchronous copy of `bytes` from src to dst on `stream` (either may be
+ *                       peer-mapped memory).  One call per copy.
+ * Ordering between the two processes is the caller's job (interprocess CUDA events plus a host-side
+ * handshake; see ditango_b200/core/peer_transport.py).  These calls allocate nothing.
+ */
+DTB_API int dtb_ipc_export_mem(const void* dev_ptr, void* handle64, int64_t* offset);
+DTB_API int dtb_ipc_open_mem(const void* handle64, void** base_ptr);
+DTB_API int dtb_ipc_close_mem(void* base_ptr);
+DTB_API int dtb_peer_copy_async(void* dst, const void* src, int64_t bytes, void* stream);
+
+/*
  * Partial attention state of a query chunk against ONE key/value chunk (non-causal, no dropout):
  *     S = scale * Q K^T,  lse = logsumexp_k S,  out = softmax_k(S) V
  * Replaces flash_attn_func(q, k, v, dropout_p=0, return_attn_probs=True) at

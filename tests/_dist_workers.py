@@ -144,7 +144,11 @@ def gpu_ring_worker(rank, world, port, case, ret):
     rm = init_redundancy_map(cfg)
     for t, d in enumerate(div):
         rm.divider_map[t, 0] = d
-    layer = proAttention(0, ps.get_isp_group())
+    group = ps.get_isp_group()
+    if case.get("transport") == "peer":
+        from ditango_b200.core.peer_transport import PeerCopyGroup
+        group = PeerCopyGroup(group, timeout_s=60.0)
+    layer = proAttention(0, group)
     layer.hop_grouping = case.get("hop_grouping", "single")
     B, S, H, D = case["B"], case["S"], case["H"], case["D"]
     data = drifting_qkv(B, S, H, D, len(div), seed=case["seed"], drift=case["drift"], dtype=torch.bfloat16)
@@ -167,6 +171,8 @@ def gpu_ring_worker(rank, world, port, case, ret):
     status = ops.read_status()
     ret[rank] = (torch.stack(outs), dict(layer.stats), uly, status)
     dist.barrier()
+    if case.get("transport") == "peer":
+        group.close()
     dist.destroy_process_group()
 
 

@@ -73,14 +73,14 @@ class LoopbackGroup:
         self._coll_seq = 0
 
     # ------------------------------------------------------------------ point to point
-    def p2p_isend(self, tensor: torch.Tensor, dst: Optional[int] = None):
+    def p2p_isend(self, tensor: torch.Tensor, dst: Optional[int] = None, slot=None):
         if dst is None:
             dst = (self.rank_in_group + 1) % self.world_size
         key = (self.rank_in_group, dst, self._send_seq[dst])
         self._send_seq[dst] += 1
         self._ops.append(("send", key, tensor))
 
-    def p2p_irecv(self, size=None, dtype=None, src: Optional[int] = None, out: Optional[torch.Tensor] = None):
+    def p2p_irecv(self, size=None, dtype=None, src: Optional[int] = None, out: Optional[torch.Tensor] = None, slot=None):
         if src is None:
             src = (self.rank_in_group - 1) % self.world_size
         tensor = out if out is not None else torch.empty(size, dtype=dtype, device=self.device)
@@ -226,3 +226,93 @@ def stepped(fabric: LoopbackFabric, rank: int, t: int):
     if rank == 0:
         update_timestep(t)
     fabric.barrier()
+
+
+# ---------------------------------------------------------------------------------------------------
+# The copy-engine transport (ditango_b200/core/peer_transport.py) on threads: same protocol code --
+# requests, sequence numbers, buffer alternation, bounded host waits -- with the platform hooks (device
+# memory, CUDA IPC, interprocess events, the shared counter table) replaced by in-process stand-ins.
+class _NullEvent:
+    def record(self, stream=None):
+        pass
+
+
+class _NullStream:
+    def wait_event(self, ev):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+def thread_peer_group(group: "LoopbackGroup", timeout_s: float = 30.0):
+    """PeerCopyGroup over a LoopbackGroup with CPU tensors: buffers are shared by reference, copies are
+    synchronous `copy_` calls, events are no-ops (every operation has completed when the host call returns)."""
+    import numpy as np
+    from ditango_b200.core.peer_transport import PeerCopyGroup
+
+    fabric = group.fabric
+
+    class ThreadPeerGroup(PeerCopyGroup):
+        def _new_stream(self):
+            return _NullStream()
+
+        def _current_stream(self):
+            return _NullStream()
+
+        def _alloc(self, shape, dtype):
+            return torch.empty(shape, dtype=dtype)
+
+        def _export_tensor(self, t):
+            return t
+
+        def _import_tensor(self, handle):
+            return handle
+
+        def _copy(self, dst, src, stream):
+            dst.copy_(src)
+
+        def _new_event(self):
+            return _NullEvent()
+
+        def _new_local_event(self):
+            return _NullEvent()
+
+        def _export_event(self, ev):
+            return ev
+
+        def _import_event(self, handle):
+            return handle
+
+        def _keep_alive(self, tensor):
+            pass
+
+        def _exchange(self, obj):
+            return _exchange_objects(self.inner, obj)
+
+        def _shared_counters(self):
+            with fabric.cv:
+                table = getattr(fabric, "peer_counters", None)
+                if table is None:
+                    n = fabric.world
+                    table = fabric.peer_counters = np.zeros((n, n, self.MAX_CHANNELS, 4), dtype=np.int64)
+            self._shm = None
+            return table
+
+    return ThreadPeerGroup(group, timeout_s=timeout_s)
+
+
+def _exchange_objects(group: "LoopbackGroup", obj):
+    """all_gather_object among the logical ranks."""
+    f = group.fabric
+    key = ("obj", group._coll_seq)
+    group._coll_seq += 1
+    with f.cv:
+        f.coll.setdefault(key, {})[group.rank_in_group] = obj
+        f.cv.notify_all()
+        f.wait_for(lambda: len(f.coll[key]) == group.world_size, f"object exchange {key}")
+        parts = [f.coll[key][r] for r in range(group.world_size)]
+    f.barrier()
+    with f.cv:
+        f.coll.pop(key, None)
+    return parts

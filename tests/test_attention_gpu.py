@@ -90,11 +90,15 @@ CASES = {
 }
 
 
-@pytest.mark.parametrize("world,grouping", [(2, "single"), (4, "single"), (8, "single"), (4, "doubling"), (8, "doubling")])
-def test_ring_attention_multi_gpu_matches_oracle(world, grouping):
+@pytest.mark.parametrize("world,grouping,transport", [(2, "single", "nccl"), (4, "single", "nccl"), (8, "single", "nccl"),
+                                                     (4, "doubling", "nccl"), (8, "doubling", "nccl"),
+                                                     (2, "single", "peer"), (4, "single", "peer"), (8, "single", "peer")])
+def test_ring_attention_multi_gpu_matches_oracle(world, grouping, transport):
+    """transport "peer": KV chunks pushed by peer-to-peer copies into CUDA-IPC-mapped buffers of the consumer
+    (core/peer_transport.py) instead of NCCL send / receive."""
     if _ngpu() < world:
         pytest.skip(f"needs {world} GPUs")
-    case = dict(CASES[world], hop_grouping=grouping)
+    case = dict(CASES[world], hop_grouping=grouping, transport=transport)
     ret = _spawn(world, case)
     data = O.drifting_qkv(case["B"], case["S"], case["H"], case["D"], len(case["dividers"]), seed=case["seed"],
                           drift=case["drift"], dtype=torch.bfloat16)

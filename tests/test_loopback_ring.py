@@ -440,3 +440,90 @@ def test_dit_with_reuse_schedule_on_one_gpu_stays_close_to_full_refresh():
     assert torch.isfinite(reuse).all()
     assert (reuse - fresh).abs().max().item() <= 0.1 * fresh.abs().max().item()
     assert ops.read_status() == 0
+
+
+# ------------------------------------------------------------------------------------------ copy-engine transport (CPU half)
+@pytest.mark.parametrize("name", ["cfg1_n2", "trace_n4", "n8", "varlen_n4"])
+def test_peer_copy_transport_protocol_reproduces_executed_reference(name, cpu_engine):
+    """The request / push / ready protocol of core/peer_transport.py (sequence numbers, alternating buffers,
+    slots shared by all sources) under the attention objects, on threads with in-process stand-ins for device
+    memory and events: the outputs are still those of the executed reference."""
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    world, B, S, H, D, seed, rs = (int(x) for x in z["meta"])
+    div = z["dividers"].tolist()
+    cu = z["cu"].tolist() if "cu" in z.files else None
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    _init_schedule(world, div)
+    from ditango_b200.core.attention import proAttention
+
+    def body(r, group, fabric):
+        layer = proAttention(0, LB.thread_peer_group(group))
+        outs = []
+        for t, (q, k, v) in enumerate(data):
+            LB.stepped(fabric, r, t)
+            lo, hi = r * S // world, (r + 1) * S // world
+            ql, kl, vl = (x[:, lo:hi].contiguous() for x in (q, k, v))
+            if cu is not None:
+                c = torch.tensor(cu[r], dtype=torch.int32)
+                o = layer.varlen_attn(ql[0], kl[0], vl[0], cu_seqlens_q=c, cu_seqlens_kv=c,
+                                      max_seqlen_q=hi - lo, max_seqlen_kv=hi - lo)[None]
+            else:
+                o = layer.attn(ql, kl, vl)
+            outs.append(o.float().clone())
+        return torch.stack(outs), dict(layer.stats)
+    res = LB.run_ranks(world, body)
+    gold = z["out"]
+    for r in range(world):
+        assert res[r][1]["chunks_received"] > 0
+        for t in range(len(div)):
+            mine = res[r][0][t]
+            if cu is not None:
+                valid = cu[r][1]
+                err = (mine[:, :valid] - torch.from_numpy(gold[t, r])[:, :valid]).abs().max().item()
+            else:
+                err = (mine[:, ::rs] - torch.from_numpy(gold[t, r])).abs().max().item()
+            assert err <= 2e-5, (name, r, t, err)
+
+
+def test_peer_copy_transport_with_pair_map(cpu_engine):
+    """Hops that are not permutations (a rank serves several consumers in one hop, ranks need different
+    numbers of hops): the per-pair request counters keep owner and consumer in step."""
+    world, T = 4, 6
+    reusable = np.random.RandomState(4).rand(T, world, world) < 0.6
+    reusable[0] = False
+    data = O.drifting_qkv(1, 32 * world, 2, 16, T, seed=7, drift=0.05)
+    _init_schedule(world, steps=T, pair_map=reusable)
+    from ditango_b200.core.attention import proAttention
+
+    def body(r, group, fabric):
+        layer = proAttention(0, LB.thread_peer_group(group))
+        outs = []
+        for t, (q, k, v) in enumerate(data):
+            LB.stepped(fabric, r, t)
+            lo, hi = r * 32, (r + 1) * 32
+            outs.append(layer.attn(*(x[:, lo:hi].contiguous() for x in (q, k, v))).clone())
+        return torch.stack(outs)
+    res = LB.run_ranks(world, body)
+    want = O.run_pair_map_group(world, reusable, data)
+    for r in range(world):
+        for t in range(T):
+            assert (res[r][t] - want[t][r]).abs().max().item() <= 2e-5
+
+
+def test_peer_copy_transport_gives_up_on_a_silent_peer(cpu_engine):
+    """A rank that posts its receive but whose owner never sends: the bounded host wait raises; nothing is
+    left waiting on a device."""
+    from ditango_b200.core.peer_transport import TransportTimeout
+
+    def body(r, group, fabric):
+        g = LB.thread_peer_group(group, timeout_s=1.0)
+        x = torch.ones(4)
+        g.p2p_prepare("kv", (x,), 1)
+        if r == 0:
+            buf = g.p2p_irecv(src=1, slot=("kv", 0, 0))
+            h = g.p2p_commit_batch()
+            with pytest.raises(TransportTimeout):
+                g.p2p_wait_batch(h)
+            return "timed out"
+        return "silent"
+    assert LB.run_ranks(2, body) == ["timed out", "silent"]
