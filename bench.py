@@ -56,10 +56,10 @@ def measured_peaks():
 
 def flash_dram_traffic(B, S_q, H, D):
     """DRAM bytes of one flash launch on a square chunk pair, scaled from the ncu captures under
-    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): 424.6 MB at B1 S14882 H24 D128 and
-    519.0 MB at B2 S8888 H48 D64.  K and V of a head stay in L2 while its query tiles run, so traffic
+    profiles/ (dram__bytes_read.sum + dram__bytes_write.sum): 423.2 MB at B1 S14882 H24 D128 and
+    517.1 MB at B2 S8888 H48 D64.  K and V of a head stay in L2 while its query tiles run, so traffic
     follows the tensor sizes (tokens x heads x head_dim), not the FLOPs."""
-    ref = {128: (424.6e6, 1 * 14882 * 24 * 128), 64: (519.0e6, 2 * 8888 * 48 * 64)}[D]
+    ref = {128: (423.2e6, 1 * 14882 * 24 * 128), 64: (517.1e6, 2 * 8888 * 48 * 64)}[D]
     return ref[0] * (B * S_q * H * D) / ref[1]
 
 
@@ -513,7 +513,8 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": round(per_launch_tflops, 2), "peak": peaks["tensor"],
                          "unit": "TFLOP/s", "frac": round(per_launch_tflops / peaks["tensor"], 4),
                          "peak_kind": f"{peaks['source']} sustained bf16 cuBLAS GEMM; burst {peaks['tensor_burst']}",
-                         "kernel": f"flash_fwd_kernel<{D}>", "launches_timed": int(n_flash),
+                         "kernel": f"flash_fwd_row_kernel<{D}>" if D == 128 else f"flash_fwd_pair_kernel<{D}>",
+                         "launches_timed": int(n_flash),
                          "traffic": round(flash_dram_traffic(B, S_loc, H, D)),
                          "traffic_kind": "bytes per launch, scaled by tensor size from the ncu capture of a smaller chunk pair"},
             "clocks": clocks,
@@ -545,6 +546,8 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        if hasattr(group, "close"):
+            group.close()
         dist.destroy_process_group()
 
 

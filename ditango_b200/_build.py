@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIBDIR, "libditango_b200.so")
 STAMP = os.path.join(LIBDIR, "build.stamp")
-SOURCES = ["capi.cu", "flash_fwd_sm100.cu", "merge_states.cu", "drift_stats.cu"]
+SOURCES = ["capi.cu", "flash_fwd_sm100.cu", "flash_fwd_row.cu", "flash_fwd_pair.cu", "merge_states.cu", "drift_stats.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -161,6 +161,11 @@ class PeerCopyGroup:
         else:
             names = self._exchange(None)
             shm = shared_memory.SharedMemory(name=names[0])
+            try:        # this process only attached: the creator unlinks the segment, nobody else should try to
+                from multiprocessing import resource_tracker
+                resource_tracker.unregister(shm._name, "shared_memory")
+            except Exception:
+                pass
         self._shm = shm
         self._shm_owner = self.rank_in_group == 0
         return np.ndarray((n, n, self.MAX_CHANNELS, 4), dtype=np.int64, buffer=shm.buf)

@@ -1,4 +1,5 @@
-// Parameters and launcher of the partial-attention forward kernel (flash_fwd_sm100.cu).
+// Parameters and launcher of the partial-attention forward kernels (flash_fwd_sm100.cu picks between
+// flash_fwd_row.cu and flash_fwd_pair.cu by head dimension).
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

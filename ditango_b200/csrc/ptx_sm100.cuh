@@ -195,25 +195,4 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// Two fp32 -> packed bf16 pair on the integer pipe: add half a bf16 ulp to each value (round to nearest,
-// ties away from zero) and pick the two upper halves with one byte permute.  cvt.rn.bf16x2.f32 gives the
-// same value up to the tie rule but is issued to the same unit as ex2, where a softmax loop has no cycles
-// to spare; this form costs three integer instructions per pair instead.  Finite inputs only.
-__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
-  const uint32_t a = __float_as_uint(lo) + 0x8000u;
-  const uint32_t b = __float_as_uint(hi) + 0x8000u;
-  return __byte_perm(a, b, 0x7632);
-}
-#ifndef DTB_ALU_PACK
-#define DTB_ALU_PACK 0
-#endif
-// bf16 pair of two probabilities (finite, non-negative)
-__device__ __forceinline__ uint32_t pack_p_bf16x2(float lo, float hi) {
-#if DTB_ALU_PACK
-  return pack_bf16x2_alu(lo, hi);
-#else
-  return pack_bf16x2(lo, hi);
-#endif
-}
-
 }  // namespace dtb
