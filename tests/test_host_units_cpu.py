@@ -182,3 +182,68 @@ def test_init_ditango_under_the_reference_package_name(tmp_path):
     mp.spawn(_init_worker, args=(2, 29871, str(cfg), ret), nprocs=2, join=True)
     for r in range(2):
         assert ret[r] == (True, 2, r, [0, 1], 2, 2, 2)
+
+
+def test_schedule_lookup_sees_writes_through_any_alias_of_the_divider_tensor():
+    """`rm.get_map()[t, l] = d` and writes through a reference held from earlier take effect on the next
+    lookup, as in the reference, where every lookup reads the tensor (core/redundancy_map.py:49-87)."""
+    from ditango_b200.core import redundancy_map as rmod
+    from ditango_b200.core.config import init_config
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = 2, 4
+    rmod.destroy_redundancy_map()
+    rm = rmod.init_redundancy_map(cfg, world_size=4)
+    held = rm.divider_map
+    assert rm.get_curr_isp_stride(1, 0) == 4
+    rm.get_map()[1, 0] = 2
+    assert rm.get_curr_isp_stride(1, 0) == 2
+    held[2, 1] = 4
+    assert rm.get_curr_isp_stride(2, 1) == 1 and rm.get_next_isp_stride(1, 1) == 1
+    rmod.destroy_redundancy_map()
+
+
+def test_cpu_profiling_branch_follows_the_reference_drift_metric():
+    """NaN positions masked, mean|cur| when the previous output is ~0, inf when nothing is valid
+    (utils.py:202-267); and switching profiling on by assignment works."""
+    import math
+    import torch
+    from oracle import ring_oracle as O
+    from ditango_b200.core import redundancy_map as rmod
+    from ditango_b200.core.config import init_config
+    from ditango_b200.utils import rel_l1
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(1000, generator=g), torch.randn(1000, generator=g)
+    a[3] = float("nan")
+    b[7] = float("nan")
+    assert abs(rel_l1(a, b) - O.rel_l1(a, b)) < 1e-12
+    assert abs(rel_l1(a, torch.zeros(1000)) - O.rel_l1(a, torch.zeros(1000))) < 1e-12
+    assert math.isinf(rel_l1(torch.full((4,), float("nan")), torch.ones(4)))
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = 1, 3
+    rmod.destroy_redundancy_map()
+    rm = rmod.init_redundancy_map(cfg, world_size=1)
+    rm.auto_setting = True                      # not through enable_auto_setting()
+    x = torch.randn(2, 8, 2, 4, generator=g)
+    y = x + 0.1 * torch.randn(2, 8, 2, 4, generator=g)
+    y[0, 0, 0, 0] = float("nan")
+    rm.record_out_redundancy(0, 0, x)
+    rm.record_out_redundancy(1, 0, y)
+    assert abs(rm.redundancy_map[1, 0].item() - O.rel_l1(y, x)) < 1e-6
+    rmod.destroy_redundancy_map()
+
+
+def test_receive_buffers_are_per_group_and_follow_the_latest_shape():
+    import torch
+    from ditango_b200.core import attention as A
+
+    class G:
+        pass
+    g1, g2 = G(), G()
+    x = torch.zeros(2, 3)
+    a = A._slot(g1, "kv0", 0, x)
+    assert A._slot(g1, "kv0", 0, x) is a and A._slot(g2, "kv0", 0, x) is not a
+    b = A._slot(g1, "kv0", 0, torch.zeros(4, 3))
+    assert b.shape == (4, 3) and sum(1 for k in A._SLOTS if k[0] == id(g1)) == 1      # the old shape is dropped
+    A.release_receive_slots(g1)
+    assert not any(k[0] == id(g1) for k in A._SLOTS) and any(k[0] == id(g2) for k in A._SLOTS)
+    A.release_receive_slots()
