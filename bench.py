@@ -761,6 +761,8 @@ def run_dit(args):
             "finite": bool(torch.isfinite(latents.float()).all().item())}), flush=True)
     if world > 1:
         dist.barrier()
+        if hasattr(group, "close"):
+            group.close()
         dist.destroy_process_group()
 
 
@@ -831,8 +833,9 @@ def main():
                     help="ditango mode: stride schedule (what the reference can express) or a per-pair reuse map")
     ap.add_argument("--hop-grouping", default="single", choices=["single", "doubling"],
                     help="transport batches per call: one per hop, or batches of 1, 2, 4, ... hops")
-    ap.add_argument("--transport", default="nccl", choices=["nccl", "peer"],
-                    help="KV hops by NCCL send/receive, or by copy-engine copies into IPC-mapped buffers of the consumer")
+    ap.add_argument("--transport", default="peer", choices=["nccl", "peer"],
+                    help="KV hops by copy-engine copies into IPC-mapped buffers of the consumer (default: no SM is taken "
+                         "from the attention kernel, full link rate per pair), or by NCCL send/receive")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity miniature that runs before the warm-up at N > 1")
