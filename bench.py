@@ -261,8 +261,8 @@ def run_ours(args):
             tp = torch.tensor([mine[k] for k in keys], device=device, dtype=torch.float64)
             dist.all_reduce(tp, op=dist.ReduceOp.MAX)
             parity = {k: float(f"{x:.3e}") for k, x in zip(keys, tp.tolist())}
-            parity["case"] = ("proAttention.attn on this job's NCCL group vs the CPU oracle, max over ranks and steps: "
-                              + json.dumps(PARITY_CASES[world]))
+            parity["case"] = (f"proAttention.attn on this job's own group (transport {args.transport}) vs the CPU "
+                              "oracle, max over ranks and steps: " + json.dumps(PARITY_CASES[world]))
             parity["within_tolerance"] = bool(parity["max_abs"] <= 2e-2 and parity["mean_abs"] <= 1e-3
                                               and parity["lse_max"] <= 1e-3 and parity["ulysses_max_abs"] <= 2e-2
                                               and parity["status"] == 0)
