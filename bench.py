@@ -639,15 +639,28 @@ def run_reference(args):
         return
     w = dict(WORKLOADS[args.workload])
     t_all = []
+    executed_failed = None
     for i in range(args.warmup + args.steps):
-        cpu = executed_reference(w, args.gpus, args.cpu_seq, args.mode)
+        cpu = None
+        if executed_failed is None:
+            try:
+                cpu = executed_reference(w, args.gpus, args.cpu_seq, args.mode)
+            except Exception as e:  # noqa: BLE001 - the arm still reports, on the port, and says why
+                executed_failed = f"{type(e).__name__}: {str(e).strip().splitlines()[-1][:200] if str(e).strip() else ''}"
         if cpu is None:
             cpu = cpu_baseline(w, args.gpus, sample_seq=args.cpu_seq, steps=1, min_seconds=4.0)
         if i >= args.warmup:
             t_all.append(cpu)
+    t_all = [c for c in t_all if c["kind"] == t_all[-1]["kind"]]
     value = statistics.mean(c["value"] for c in t_all)
     cpu = dict(t_all[-1], value=round(value, 4))
-    c1 = config1_reference()
+    if executed_failed is not None:
+        cpu["executed_reference_failed"] = executed_failed
+    try:
+        c1 = config1_reference()
+    except Exception as e:  # noqa: BLE001
+        c1 = None
+        cpu["config1_failed"] = f"{type(e).__name__}"
     if c1 is not None:
         cpu["config1"] = c1
     B, H, D, S = w["B"], w["H"], w["D"], w["S"]

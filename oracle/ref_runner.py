@@ -94,14 +94,40 @@ def _worker(rank, world, case, port, ret):
     dist.destroy_process_group()
 
 
-def time_reference(world, case, port=29790):
+def time_reference(world, case, port=29790, limit_s=600.0):
     """Runs the reference's proAttention.attn for len(case['dividers']) steps of one layer on `world` gloo
     ranks (world >= 2: the reference has no attention group at one rank).  Returns
     dict(seconds, flops, steps, cores)."""
     assert world >= 2 and available()
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, case, port + int(time.time()) % 97, ret), nprocs=world, join=True)
+    # The ranks are CPU processes: hide any GPU from them (the reference would otherwise put its receive
+    # buffers on cuda:<rank>), and keep a launcher's rendezvous variables out of their environment.
+    # (TORCHELASTIC_USE_AGENT_STORE would make rank 0 of the CPU group look for the launcher's store instead of
+    # opening its own.)
+    names = ["CUDA_VISIBLE_DEVICES", "MASTER_ADDR", "MASTER_PORT", "WORLD_SIZE", "RANK", "LOCAL_RANK",
+             "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE", "OMP_NUM_THREADS"]
+    names += [k for k in os.environ if k.startswith("TORCHELASTIC_")]
+    saved = {k: os.environ.get(k) for k in names}
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""
+    for k in saved:
+        if k != "CUDA_VISIBLE_DEVICES":
+            os.environ.pop(k, None)
+    try:
+        ctx = mp.spawn(_worker, args=(world, case, port + int(time.time()) % 97, ret), nprocs=world, join=False)
+        deadline = time.time() + limit_s
+        while not ctx.join(timeout=5.0):
+            if time.time() > deadline:
+                for p in ctx.processes:          # the exact children started above
+                    if p.is_alive():
+                        p.terminate()
+                raise TimeoutError(f"the reference's CPU ranks did not finish within {limit_s:.0f} s")
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
     secs = max(ret[r][0] for r in range(world))
     flops = sum(ret[r][1] for r in range(world))
     return dict(seconds=secs, flops=flops, steps=len(case["dividers"]), cores=os.cpu_count() or 1)
