@@ -275,6 +275,7 @@ def run_ours(args):
         rm._refine_divider_map()
         rm.screen_self_sends()
     proAttention.hop_grouping = args.hop_grouping
+    proAttention.chain_launches = bool(args.chain)
     layers = [proAttention(l, group) for l in range(w["layers"])]
     raw, gen = make_inputs(w, rank, world, device)
     B, H, D, S = w["B"], w["H"], w["D"], w["S"]
@@ -506,7 +507,8 @@ def run_ours(args):
                        "reuse_probability": w["p"] if (args.mode == "ditango" and world > 1) else 0.0,
                        "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none",
                        "hop_grouping": args.hop_grouping if (args.mode != "ulysses" and world > 1) else "none",
-                       "transport": args.transport if (args.mode != "ulysses" and world > 1) else "none"},
+                       "transport": args.transport if (args.mode != "ulysses" and world > 1) else "none",
+                       "chain_launches": bool(args.chain and args.mode != "ulysses" and world > 1)},
             "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
             "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
             "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
@@ -515,6 +517,8 @@ def run_ours(args):
                          "peak_kind": f"{peaks['source']} sustained bf16 cuBLAS GEMM; burst {peaks['tensor_burst']}",
                          "kernel": f"flash_fwd_row_kernel<{D}>" if D == 128 else f"flash_fwd_pair_kernel<{D}>",
                          "launches_timed": int(n_flash),
+                         "timed_unit": ("one launch, or one chain of overlapping launches (FLOPs of the chain over its "
+                                        "duration)") if (args.chain and world > 1) else "one launch",
                          "traffic": round(flash_dram_traffic(B, S_loc, H, D)),
                          "traffic_kind": "bytes per launch, scaled by tensor size from the ncu capture of a smaller chunk pair"},
             "clocks": clocks,
@@ -724,6 +728,7 @@ def run_dit(args):
         rm.screen_self_sends()
     torch.manual_seed(0)
     proAttention.hop_grouping = args.hop_grouping
+    proAttention.chain_launches = bool(args.chain)
     with torch.device(device):
         model = CogVideoXDiT(dcfg, group, mode=args.mode).to(torch.bfloat16)
     g = torch.Generator(device=device).manual_seed(0)
@@ -797,6 +802,40 @@ def run_micro(args):
         lse = torch.empty(B, H, S, device=dev, dtype=torch.float32)
         fn = lambda: ops.flash_partial(q, k, v, out=out, lse=lse)
         work, unit, peak, bound = 4.0 * B * H * S * S * D, "TFLOP/s", peaks["tensor_burst"], "tensor"
+    elif args.micro == "chain":
+        # One layer call's worth of foreign chunks: n launches folded into one state, first without and then with
+        # each launch allowed to overlap the end of the one before it.
+        n = args.states
+        q = rnd(B, S, H, D, dt=torch.bfloat16)
+        kv = [(rnd(B, S, H, D, dt=torch.bfloat16), rnd(B, S, H, D, dt=torch.bfloat16)) for _ in range(n)]
+        out = torch.empty(B, S, H, D, device=dev, dtype=torch.float32)
+        lse = torch.empty(B, S, H, device=dev, dtype=torch.float32)
+
+        def chain(overlap):
+            ops.flash_partial(q, kv[0][0], kv[0][1], out=out, lse=lse, lse_layout=ops.LSE_BSH)
+            for kk, vv in kv[1:]:
+                ops.flash_partial(q, kk, vv, out=out, lse=lse, accumulate=True, lse_layout=ops.LSE_BSH,
+                                  overlap_previous=overlap)
+        res = {}
+        for overlap in (False, True):
+            for _ in range(max(1, args.warmup)):
+                chain(overlap)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(max(1, args.steps)):
+                chain(overlap)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / max(1, args.steps)
+            res["overlapped" if overlap else "separate"] = {
+                "ms": round(ms, 4), "tflops": round(4.0 * B * H * S * S * D * n / (ms * 1e-3) / 1e12, 1)}
+            ref = (out.clone(), lse.clone()) if not overlap else ref
+        same = bool(torch.equal(ref[0], out) and torch.equal(ref[1], lse))
+        print(json.dumps({"micro": "chain", "workload": args.workload, "shape": dict(B=B, S=S, H=H, D=D), "launches": n,
+                          **res, "speedup": round(res["separate"]["ms"] / res["overlapped"]["ms"], 4),
+                          "bit_identical": same, "peak_burst": peaks["tensor_burst"], "status": ops.read_status()}), flush=True)
+        return
     elif args.micro == "merge":
         n = args.states
         lay = ops.LSE_BSH if args.lse_layout == "bsh" else ops.LSE_BHS
@@ -849,13 +888,16 @@ def main():
     ap.add_argument("--transport", default="peer", choices=["nccl", "peer"],
                     help="KV hops by copy-engine copies into IPC-mapped buffers of the consumer (default: no SM is taken "
                          "from the attention kernel, full link rate per pair), or by NCCL send/receive")
+    ap.add_argument("--chain", action="store_true",
+                    help="ditango / ring mode at N > 1: own chunk first, wait for all incoming chunks, then the remaining "
+                         "attention launches back to back, each overlapping the end of the one before it")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity miniature that runs before the warm-up at N > 1")
     ap.add_argument("--no-plain-ring", action="store_true", help="skip the plain-ring comparison pass at N > 1")
-    ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy"], help="time one kernel and exit")
+    ap.add_argument("--micro", default=None, choices=["flash", "merge", "copy", "chain"], help="time one kernel and exit")
     ap.add_argument("--shard", type=int, default=8, help="--micro: tokens = S / shard")
-    ap.add_argument("--states", type=int, default=4, help="--micro merge: number of states")
+    ap.add_argument("--states", type=int, default=4, help="--micro merge: number of states; --micro chain: launches per chain")
     ap.add_argument("--lse-layout", default="bsh", choices=["bsh", "bhs"],
                     help="--micro merge: lse as [B,S,H] (what the attention path keeps internally) or [B,H,S]")
     args = ap.parse_args()

@@ -15,12 +15,13 @@ _lib = None
 DTB_F32, DTB_BF16 = 0, 1
 LSE_BHS, LSE_BSH = 0, 1
 MERGE_MAX_STATES = 16
+LAUNCH_OVERLAP_PREVIOUS = 1
 
 EXPORTS = (
     "dtb_version", "dtb_last_error", "dtb_device_supported", "dtb_read_status",
     "dtb_peek_status_async", "dtb_post_status",
     "dtb_ipc_export_mem", "dtb_ipc_open_mem", "dtb_ipc_close_mem", "dtb_peer_copy_async",
-    "dtb_flash_fwd", "dtb_merge_states", "dtb_copy_chunks",
+    "dtb_flash_fwd", "dtb_flash_fwd_ex", "dtb_merge_states", "dtb_copy_chunks",
     "dtb_drift_scratch_bytes", "dtb_drift_accumulate",
     "dtb_drift_noalloc_max_elements", "dtb_drift_accumulate_noalloc",
 )
@@ -67,6 +68,8 @@ def load():
         c_void_p, c_int, c_int64, c_void_p, c_int, c_int,
         c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
         c_int, c_int, c_float, c_void_p]
+    lib.dtb_flash_fwd_ex.restype = c_int
+    lib.dtb_flash_fwd_ex.argtypes = lib.dtb_flash_fwd.argtypes[:-1] + [c_int, c_void_p]
     lib.dtb_merge_states.restype = c_int
     lib.dtb_merge_states.argtypes = [
         c_int, POINTER(c_void_p), POINTER(c_int), POINTER(c_void_p), POINTER(c_int),

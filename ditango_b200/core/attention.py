@@ -76,6 +76,14 @@ class proAttention:
     # dtype of the values of cached block states (the reference keeps fp32: utils.py:76); bfloat16 halves
     # the cache's footprint and read traffic.  lse stays fp32.
     cache_dtype = torch.float32
+    # Overlapping attention launches.  The chunks of a call are attended by one launch each, and a launch's
+    # grid rarely divides evenly over the SMs, so each ends in a partly filled wave.  With True the own chunk
+    # is attended first, then ALL incoming chunks of the call are waited for, then the remaining launches are
+    # queued back to back with nothing between them on the stream, each allowed to start while the one
+    # before it is finishing (ops.flash_partial(overlap_previous=True)).  The price: no chunk is attended
+    # before the last one has arrived, so it pays where transfers are short against the own chunk's launch.
+    # Every rank of a group must agree.
+    chain_launches = False
 
     def __init__(self, layer_id: int, isp_group):
         self.group = isp_group
@@ -106,8 +114,11 @@ class proAttention:
         self._have = [set() for _ in range(self.isp_size)]
         self._last_lse: Optional[torch.Tensor] = None      # [B,S,H] / [T,H] of the last result
         self.stats = dict(calls=0, chunks_attended=0, chunks_received=0, bytes_received=0,
-                          cached_blocks_merged=0, merge_launches=0)
+                          cached_blocks_merged=0, merge_launches=0, overlapped_launches=0)
         self._comm_events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = []
+        # True while the operation queued last on the compute stream by this object is an attention launch
+        # (what overlap_previous requires of its predecessor)
+        self._chain_open = False
 
     @property
     def last_lse(self) -> Optional[torch.Tensor]:
@@ -176,6 +187,7 @@ class proAttention:
     def _wait_hop(self, handle):
         if handle is None:          # covered by the batch of an earlier hop
             return
+        self._chain_open = False    # a wait (or the transport's copy) now sits behind the last launch
         if self.measure_comm and torch.cuda.is_available():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -184,6 +196,23 @@ class proAttention:
             self._comm_events.append((a, b))
         else:
             self.group.p2p_wait_batch(handle)
+
+    def _attend(self, chain: bool, query, kk, vv, **kw):
+        """One attention launch; in chain mode it overlaps the previous one when that was an attention launch
+        of this object with nothing queued on the stream since."""
+        if chain and self._chain_open:
+            kw["overlap_previous"] = True
+        self.stats["chunks_attended"] += 1
+        self.stats["overlapped_launches"] += int("overlap_previous" in kw)
+        res = _engine.flash_partial(query, kk, vv, lse_layout=LSE_BSH, **kw)
+        self._chain_open = True
+        return res
+
+    @staticmethod
+    def _chain_timing(begin: bool):
+        log = getattr(_engine, "LaunchLog", None)
+        if log is not None:
+            (log.chain_begin if begin else log.chain_end)()
 
     def exposed_comm_ms(self, reset: bool = True) -> float:
         """Time the compute stream spent blocked on incoming KV since the last reset."""
@@ -203,22 +232,31 @@ class proAttention:
         packed = cu_q is not None
         payload = (key, value, cu_kv) if packed else (key, value)
 
+        chain = bool(self.chain_launches)
+        self._chain_open = False
+
         def attend(kv, keep=False):
             kw = {}
             if packed:
                 kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
-            self.stats["chunks_attended"] += 1
-            return _engine.flash_partial(query, kv[0], kv[1], lse_layout=LSE_BSH,
-                                         out_dtype=self.cache_dtype if keep else torch.float32, **kw)
+            return self._attend(chain, query, kv[0], kv[1], out_dtype=self.cache_dtype if keep else torch.float32, **kw)
 
         plan = plan_pair_step(N, flags, self._have)
         posted = self._post_hops(plan, plan.n_hops, payload)
         own = attend(payload)
+        if chain:
+            for hop in range(plan.n_hops):
+                self._wait_hop(posted[hop][1])
+            self._chain_timing(True)
         for hop in range(plan.n_hops):
             current, handle = posted[hop]
-            self._wait_hop(handle)
+            if not chain:
+                self._wait_hop(handle)
             if current is not None:
                 self._chunk_states[plan.ranks[me].owners[hop]] = attend(current, keep=True)
+        if chain:
+            self._chain_timing(False)
+        self._chain_open = False
         others = [(o, l, LSE_BSH) for src in ((me + i) % N for i in range(1, N))
                   for o, l in (self._chunk_states.get(src, (None, None)),) if l is not None]
         self.stats["cached_blocks_merged"] += len(others) - len(plan.ranks[me].owners)
@@ -262,16 +300,17 @@ class proAttention:
         keep_chunks = stride == N and next_stride != N        # fine-grained store after a full refresh
         keep_block = stride != N and next_stride != N
 
+        chain = bool(self.chain_launches) and N > 1
+        self._chain_open = False
+
         def attend(kv, into=None, dtype=torch.float32):
             kk, vv = kv[0], kv[1]
             kw = {}
             if packed:
                 kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=kv[2], max_seqlen_q=max_q, max_seqlen_k=max_kv)
-            self.stats["chunks_attended"] += 1
             if into is None:
-                return _engine.flash_partial(query, kk, vv, lse_layout=LSE_BSH, out_dtype=dtype, **kw)
-            return _engine.flash_partial(query, kk, vv, out=into[0], lse=into[1], accumulate=True,
-                                         lse_layout=LSE_BSH, **kw)
+                return self._attend(chain, query, kk, vv, out_dtype=dtype, **kw)
+            return self._attend(chain, query, kk, vv, out=into[0], lse=into[1], accumulate=True, **kw)
 
         # 1. cached blocks (every block but the target one)
         states = []
@@ -289,8 +328,14 @@ class proAttention:
         # A single rank with nothing to merge gets its bf16 result straight from the attention kernel.
         direct16 = N == 1 and self.output_dtype == torch.bfloat16 and not rmap.is_auto_setting()
         own = None
-        if mine.own_first:
-            own = attend(payload)          # target block is a foreign one: own chunk first, overlapping hop 0
+        if mine.own_first or chain:
+            # target block is a foreign one: own chunk first, overlapping hop 0.  Chained launches: always first,
+            # so that the transfers run under it and every wait sits in front of the launches that overlap.
+            own = attend(payload)
+        if chain:
+            for hop in range(stride):
+                self._wait_hop(posted[hop][1])
+            self._chain_timing(True)
 
         # 3. the target block's chunks.  A state that goes to the cache without further accumulation is
         #    written by the attention kernel in the cache's dtype: no cast pass afterwards.
@@ -299,17 +344,25 @@ class proAttention:
         fresh_chunks = sum(1 for o in mine.owners if o != me)
         for hop in range(stride):
             current, handle = posted[hop]
-            self._wait_hop(handle)
+            if not chain:
+                self._wait_hop(handle)
             if mine.owners[hop] == me:
-                own = attend(payload, dtype=torch.bfloat16 if direct16 else torch.float32)
+                if own is None:            # (chained launches attended it before the waits)
+                    own = attend(payload, dtype=torch.bfloat16 if direct16 else torch.float32)
             elif keep_chunks:
                 st = attend(current, dtype=self.cache_dtype)
+                if st[0].dtype != self.cache.store_dtype:
+                    self._chain_open = False           # store_block converts: a kernel behind the launch
                 self.cache.store_block(mine.owners[hop], st[0], st[1])
                 chunk_states.append((st[0], st[1], LSE_BSH))
             elif keep_block:
                 fresh = attend(current, into=fresh, dtype=self.cache_dtype if fresh_chunks == 1 else torch.float32)
             else:
                 own = attend(current, into=own)          # nothing is kept: fold into the result
+
+        if chain:
+            self._chain_timing(False)
+        self._chain_open = False
 
         # 4. store the fresh block, combine everything in one pass
         if fresh is not None:

@@ -266,13 +266,14 @@ DTB_API int dtb_peer_copy_async(void* dst, const void* src, int64_t bytes, void*
   return DTB_OK;
 }
 
-DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
-                  int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
-                  void* out, int out_dtype, int64_t out_tok_stride,
-                  float* lse, int lse_layout, int accumulate,
-                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                  int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
-                  int num_heads, int head_dim, float softmax_scale, void* stream) {
+static int flash_fwd_impl(const void* q, const void* k, const void* v,
+                          int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
+                          void* out, int out_dtype, int64_t out_tok_stride,
+                          float* lse, int lse_layout, int accumulate,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                          int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
+                          int num_heads, int head_dim, float softmax_scale, int launch_flags, void* stream) {
+  if (launch_flags & ~DTB_LAUNCH_OVERLAP_PREVIOUS) return fail(DTB_ERR_ARG, "dtb_flash_fwd: unknown launch flag 0x%x", launch_flags);
   if (!q || !k || !v || !out || !lse) return fail(DTB_ERR_ARG, "dtb_flash_fwd: null tensor pointer");
   if (head_dim != 64 && head_dim != 128) return fail(DTB_ERR_ARG, "dtb_flash_fwd: head_dim %d not in {64, 128}", head_dim);
   if (num_heads < 1 || num_heads > 65535) return fail(DTB_ERR_ARG, "dtb_flash_fwd: num_heads %d out of range", num_heads);
@@ -322,10 +323,35 @@ DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
   p.out_dtype = out_dtype;
   p.lse_layout = lse_layout;
   p.accumulate = accumulate ? 1 : 0;
+  p.overlap_previous = (launch_flags & DTB_LAUNCH_OVERLAP_PREVIOUS) ? 1 : 0;
   cudaError_t e = (head_dim == 64) ? dtb::launch_flash<64>(tq, tk, tv, p, static_cast<cudaStream_t>(stream))
                                    : dtb::launch_flash<128>(tq, tk, tv, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(DTB_ERR_CUDA, "dtb_flash_fwd launch failed: %s", cudaGetErrorString(e));
   return DTB_OK;
+}
+
+DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
+                  int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
+                  void* out, int out_dtype, int64_t out_tok_stride,
+                  float* lse, int lse_layout, int accumulate,
+                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                  int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
+                  int num_heads, int head_dim, float softmax_scale, void* stream) {
+  return flash_fwd_impl(q, k, v, q_tok_stride, k_tok_stride, v_tok_stride, out, out_dtype, out_tok_stride, lse, lse_layout,
+                        accumulate, cu_seqlens_q, cu_seqlens_k, nseg, seqlen_q, seqlen_k, total_q, total_k, num_heads,
+                        head_dim, softmax_scale, 0, stream);
+}
+
+DTB_API int dtb_flash_fwd_ex(const void* q, const void* k, const void* v,
+                     int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
+                     void* out, int out_dtype, int64_t out_tok_stride,
+                     float* lse, int lse_layout, int accumulate,
+                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                     int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
+                     int num_heads, int head_dim, float softmax_scale, int launch_flags, void* stream) {
+  return flash_fwd_impl(q, k, v, q_tok_stride, k_tok_stride, v_tok_stride, out, out_dtype, out_tok_stride, lse, lse_layout,
+                        accumulate, cu_seqlens_q, cu_seqlens_k, nseg, seqlen_q, seqlen_k, total_q, total_k, num_heads,
+                        head_dim, softmax_scale, launch_flags, stream);
 }
 
 DTB_API int dtb_merge_states(int nstates, const void* const* outs, const int* out_dtypes,

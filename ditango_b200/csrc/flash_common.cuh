@@ -71,6 +71,7 @@ __device__ __forceinline__ void write_empty_rows(const FlashParams& p, int seg, 
   if (p.accumulate || threadIdx.x >= kQT * kBM) return;
   const int q_pos = q0 + threadIdx.x;
   if (q_pos >= q_len) return;
+  grid_dependency_wait();      // the launch before this one may still be writing the same buffers
   const int64_t tok = static_cast<int64_t>(q_begin) + q_pos;
   p.lse[lse_index(p, seg, head, q_pos, tok)] = -INFINITY;
   if (p.out_dtype == 0) {
@@ -134,6 +135,24 @@ __device__ __forceinline__ void merge_weights(bool accumulate, float lse_old, fl
     w_old = e_old / tot;
     w_new = (e_new / tot) / l_row;
   }
+}
+
+// Host: one launch of an attention kernel, with the programmatic-stream-serialization attribute when the caller
+// allows the launch to overlap the end of the one before it.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_attention_kernel(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem_bytes,
+                                           cudaStream_t stream, bool overlap_previous, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_previous ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
 }
 
 }  // namespace flash

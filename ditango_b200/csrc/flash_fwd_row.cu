@@ -103,6 +103,7 @@ flash_fwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (q0 >= q_len) return;
   const int n_tiles = (k_len + kBN - 1) / kBN;
   if (n_tiles <= 0) {
+    grid_dependency_wait();      // (also when nothing is written: a grid must not complete before the one it overlaps)
     write_empty_rows<D>(p, seg, head, q_begin, q_len, q0);
     return;
   }
@@ -135,6 +136,9 @@ flash_fwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tc_fence_before();
   // CTA-uniform view of the status word: a CTA that starts after a failure elsewhere does no work.
   const int aborted = __syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0);
+  // From here on a launch queued behind this one with the overlap attribute may fill idle SMs (it takes effect
+  // once every CTA of this grid has got this far); it waits for this grid's completion before it touches results.
+  grid_launch_dependents();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
@@ -366,6 +370,9 @@ flash_fwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
 
     if (ok) ok = wait_or_abort(o_final, 0, p.status, 41);
+    // Results: the launch before this one (which may still be running if this launch overlaps it) must have
+    // completed before its state is read for accumulation or its buffers are written.
+    grid_dependency_wait();
     if (ok) {
       tc_fence_after();
       const int q_pos = q0 + tile * kBM + row;
@@ -390,6 +397,9 @@ flash_fwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }
 
   // ------------------------------------------------------------------ tear-down
+  // No CTA leaves before the launch it may overlap has completed: a launch that overlaps THIS one waits for this
+  // grid only, and relies on this grid's completion implying that of everything before it.
+  grid_dependency_wait();
   if (*reinterpret_cast<volatile int*>(p.status) != 0) __nanosleep(1000000);   // let copies in flight land
   tc_fence_before();
   __syncthreads();
@@ -416,8 +426,7 @@ cudaError_t launch_flash_row(const CUtensorMap& tq, const CUtensorMap& tk, const
     }
   }
   dim3 grid((p.seqlen_q + kQT * kBM - 1) / (kQT * kBM), p.num_heads, p.nseg);
-  flash_fwd_row_kernel<D><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, p);
-  return cudaGetLastError();
+  return launch_attention_kernel(flash_fwd_row_kernel<D>, grid, kThreads, C::kSmemBytes, stream, p.overlap_previous != 0, tq, tk, tv, p);
 }
 
 #ifdef DTB_FLASH_TIMING

@@ -23,8 +23,13 @@ struct FlashParams {
   int out_dtype;           // 0 fp32, 1 bf16
   int lse_layout;          // 0 [B,H,S] (packed: [H,T]), 1 [B,S,H]
   int accumulate;          // merge into the state already in (out, lse)
+  int overlap_previous;    // host only: launch with programmatic stream serialization (see launch_flash)
 };
 
+// With p.overlap_previous the launch may begin while the previous launch on `stream` is finishing (its CTAs fill
+// the SMs that kernel's last wave leaves idle).  The kernels read q, k, v, cu_seqlens before they wait for that
+// kernel and touch (out, lse) only after it has completed, so this is allowed exactly when the previous operation
+// on the stream is another launch_flash whose results this launch does not read as q, k, v or cu_seqlens.
 template <int D>
 cudaError_t launch_flash(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                          const FlashParams& p, cudaStream_t stream);

@@ -168,6 +168,13 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it on the stream is still running, once every CTA of that kernel has executed
+// launch_dependents (or exited); dependency_wait then blocks until that kernel has completed and its writes are
+// visible.  Both are no-ops in a launch without the attribute / without such a successor.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

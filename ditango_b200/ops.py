@@ -19,11 +19,35 @@ class LaunchLog:
     a benchmark can read per-launch device time and the FLOPs each launch executed."""
     count = 0
     events = None            # list of (start_event, end_event, flops) while enabled
+    overlapped = 0           # flash launches made with overlap_previous
+    _chain = None            # [start_event, flops] while a chain of overlapping launches is being timed as one
 
     @classmethod
     def reset(cls, with_events: bool = False):
         cls.count = 0
+        cls.overlapped = 0
         cls.events = [] if with_events else None
+        cls._chain = None
+
+    @classmethod
+    def chain_begin(cls):
+        """Launches that overlap one another cannot be timed one by one (an event between two of them would
+        also sit between the kernels on the stream): from here to chain_end() the flash launches are timed
+        as ONE entry of `events`, with their FLOPs added up."""
+        if cls.events is not None and cls._chain is None:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+            cls._chain = [start, 0.0]
+
+    @classmethod
+    def chain_end(cls):
+        if cls._chain is not None:
+            start, flops = cls._chain
+            cls._chain = None
+            if flops > 0:
+                end = torch.cuda.Event(enable_timing=True)
+                end.record()
+                cls.events.append((start, end, flops))
 
 
 def _stream_ptr() -> int:
@@ -94,13 +118,18 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                   accumulate: bool = False, out_dtype: torch.dtype = torch.float32,
                   lse_layout: int = LSE_BHS, softmax_scale: Optional[float] = None,
                   cu_seqlens_q: Optional[torch.Tensor] = None, cu_seqlens_k: Optional[torch.Tensor] = None,
-                  max_seqlen_q: Optional[int] = None, max_seqlen_k: Optional[int] = None
-                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+                  max_seqlen_q: Optional[int] = None, max_seqlen_k: Optional[int] = None,
+                  overlap_previous: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Attention state of q against one KV chunk.
 
     Dense: q [B,Sq,H,D], k,v [B,Sk,H,D] bf16.  Packed (cu_seqlens given): q [Tq,H,D], k,v [Tk,H,D].
     Returns (out, lse); with accumulate=True the chunk's state is merged into the given fp32
     (out, lse) in place.  lse is [B,H,Sq] / [H,Tq] (LSE_BHS) or [B,Sq,H] / [Tq,H] (LSE_BSH).
+
+    overlap_previous=True lets the launch start while the launch queued just before it on the current stream
+    is finishing (DTB_LAUNCH_OVERLAP_PREVIOUS).  Only pass it when that operation was another flash_partial
+    call and nothing else -- no copy, event wait or other kernel -- was queued on the stream since, and when
+    q, k, v, cu_seqlens were not written by that call; (out, lse) may be the state that call wrote.
     """
     lib = _capi.load()
     _need_cuda(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k)
@@ -140,21 +169,27 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise _capi.ExtensionError("out must be float32 or bfloat16")
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    # dense: every query row meets every key row of its sequence; packed: upper bound by maxima
+    flops = 4.0 * nseg * H * sq * sk * D
     ev = None
-    if LaunchLog.events is not None:
+    if LaunchLog._chain is not None:
+        LaunchLog._chain[1] += flops
+    elif LaunchLog.events is not None:
+        if overlap_previous:
+            raise _capi.ExtensionError("per-launch timing needs LaunchLog.chain_begin() around overlapping launches")
         ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         ev[0].record()
-    rc = lib.dtb_flash_fwd(
+    rc = lib.dtb_flash_fwd_ex(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), _tok_stride(q), _tok_stride(k), _tok_stride(v),
         out.data_ptr(), odt, _tok_stride(out), lse.data_ptr(), lse_layout, int(accumulate),
         cu_seqlens_q.data_ptr() if packed else None, cu_seqlens_k.data_ptr() if packed else None,
-        nseg, sq, sk, Tq, Tk, H, D, scale, _stream_ptr())
-    _capi.check(rc, "dtb_flash_fwd")
+        nseg, sq, sk, Tq, Tk, H, D, scale, _capi.LAUNCH_OVERLAP_PREVIOUS if overlap_previous else 0, _stream_ptr())
+    _capi.check(rc, "dtb_flash_fwd_ex")
     LaunchLog.count += 1
+    LaunchLog.overlapped += int(bool(overlap_previous))
     if ev is not None:
         ev[1].record()
-        # dense: every query row meets every key row of its sequence; packed: upper bound by maxima
-        LaunchLog.events.append((ev[0], ev[1], 4.0 * nseg * H * sq * sk * D))
+        LaunchLog.events.append((ev[0], ev[1], flops))
     return out, lse
 
 

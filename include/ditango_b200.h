@@ -131,6 +131,29 @@ DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
                   int num_heads, int head_dim, float softmax_scale, void* stream);
 
 /*
+ * dtb_flash_fwd with launch flags.  The reference walks the chunks of a ring block with one attention call
+ * per chunk (core/attention.py:160-196); on the device these are back-to-back launches whose grids do not
+ * divide evenly over the SMs, so every launch ends with a partly filled wave.
+ *
+ *  DTB_LAUNCH_OVERLAP_PREVIOUS   this launch may start while the operation queued just before it on `stream`
+ *      is finishing: its CTAs take the SMs that launch's last wave leaves idle (programmatic dependent
+ *      launch).  The kernel reads q, k, v and cu_seqlens at once, and waits for the previous launch to
+ *      complete before it reads or writes (out, lse) -- so accumulating into the state the previous launch
+ *      wrote is fine.  Contract: the operation queued just before this call on `stream` must be another
+ *      dtb_flash_fwd / dtb_flash_fwd_ex launch, and this call's q, k, v, cu_seqlens must not be produced by
+ *      it.  With anything else in between (a copy, an event wait, another kernel) pass 0: inputs written
+ *      by the operation just before are only guaranteed visible to a launch without the flag.
+ */
+#define DTB_LAUNCH_OVERLAP_PREVIOUS 1
+DTB_API int dtb_flash_fwd_ex(const void* q, const void* k, const void* v,
+                     int64_t q_tok_stride, int64_t k_tok_stride, int64_t v_tok_stride,
+                     void* out, int out_dtype, int64_t out_tok_stride,
+                     float* lse, int lse_layout, int accumulate,
+                     const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                     int nseg, int seqlen_q, int seqlen_k, int64_t total_q, int64_t total_k,
+                     int num_heads, int head_dim, float softmax_scale, int launch_flags, void* stream);
+
+/*
  * N-way merge of partial softmax states in one pass over HBM:
  *     lse_out = log sum_i exp(lse_i),   out = sum_i exp(lse_i - lse_out) * out_i
  * Replaces the chains of update_out_and_lse (utils.py:24-84) at core/attention.py:110-116, :144,

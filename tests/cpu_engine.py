@@ -9,13 +9,26 @@ from oracle import ring_oracle as O
 
 LSE_BHS, LSE_BSH = 0, 1
 
+# Per-thread record of what a rank queued on its (imaginary) stream, for tests of the launch-overlap
+# contract: ("flash", overlap_previous) for attention launches, (kind, None) for everything else.  A
+# transport stand-in reports its waits with log_op("wait").
+OP_LOG = None            # dict thread id -> list while enabled
+
+
+def log_op(kind, flag=None):
+    if OP_LOG is not None:
+        import threading
+        OP_LOG.setdefault(threading.get_ident(), []).append((kind, flag))
+
 
 def _to_bhs(lse, layout):
     return lse if layout == LSE_BHS else lse.transpose(-1, -2)
 
 
 def flash_partial(q, k, v, *, out=None, lse=None, accumulate=False, out_dtype=torch.float32, lse_layout=LSE_BHS,
-                  softmax_scale=None, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None):
+                  softmax_scale=None, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None,
+                  overlap_previous=False):
+    log_op("flash", bool(overlap_previous))
     if cu_seqlens_q is not None:
         o, l = O.partial_attention_varlen(q, k, v, cu_seqlens_q.tolist(), cu_seqlens_k.tolist(),
                                           softmax_scale=softmax_scale, out_dtype=torch.float32)
@@ -37,6 +50,7 @@ def flash_partial(q, k, v, *, out=None, lse=None, accumulate=False, out_dtype=to
 
 def merge_states(states, *, out=None, lse_out=None, lse_out_layout=LSE_BSH, out_bf16=None, want_lse=True,
                  fp32_out=True):
+    log_op("merge")
     o = l = None
     for so, sl, lay in states:
         o, l = O.merge_states(o, l, so.clone(), _to_bhs(sl, lay).clone())
@@ -60,6 +74,7 @@ def merge_states(states, *, out=None, lse_out=None, lse_out_layout=LSE_BSH, out_
 
 
 def copy_chunks(pairs, chunk_bytes, extents, src_strides, dst_strides):
+    log_op("copy")
     n0, n1, n2 = extents
     for src, dst in pairs:
         # raw-pointer semantics: offsets may reach beyond the given view into its buffer

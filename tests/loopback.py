@@ -103,6 +103,12 @@ class LoopbackGroup:
         """Receives first (they depend only on the peers having posted), then wait until every send of
         the batch has been picked up, so the sender's tensors stay untouched until they were copied."""
         f = self.fabric
+        if ops:
+            try:                                   # the CPU engine's op record, when a test has switched it on
+                from tests.cpu_engine import log_op
+                log_op("wait")
+            except ImportError:
+                pass
         for kind, key, tensor in ops or []:
             if kind != "recv":
                 continue

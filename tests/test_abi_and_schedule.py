@@ -30,6 +30,8 @@ def test_rejected_arguments_do_not_need_a_gpu():
     lib = _capi.load()
     rc = lib.dtb_flash_fwd(None, None, None, 0, 0, 0, None, 0, 0, None, 0, 0, None, None, 1, 1, 1, 1, 1, 1, 64, 1.0, None)
     assert rc == -1 and b"null" in lib.dtb_last_error()
+    rc = lib.dtb_flash_fwd_ex(None, None, None, 0, 0, 0, None, 0, 0, None, 0, 0, None, None, 1, 1, 1, 1, 1, 1, 64, 1.0, 6, None)
+    assert rc == -1 and b"launch flag" in lib.dtb_last_error()
 
 
 def test_cpu_tensors_are_refused_without_fallback():

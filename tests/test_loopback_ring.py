@@ -122,6 +122,71 @@ def test_loopback_collectives(cpu_engine):
         assert torch.equal(got, torch.full((3,), float((r - 1) % world)))
 
 
+def _check_overlap_contract(log):
+    """Every launch made with overlap_previous must directly follow another attention launch of the same rank:
+    nothing else (a wait for incoming KV, a merge, a copy) may have been queued in between."""
+    overlapped = 0
+    for ops_of_rank in log.values():
+        for i, (kind, flag) in enumerate(ops_of_rank):
+            if kind == "flash" and flag:
+                overlapped += 1
+                assert i > 0 and ops_of_rank[i - 1][0] == "flash", ops_of_rank[max(0, i - 3):i + 1]
+    return overlapped
+
+
+@pytest.mark.parametrize("name", ["cfg1_n2", "trace_n4", "n8", "varlen_n4"])
+def test_chained_launches_reproduce_executed_reference_and_keep_the_overlap_contract(name, cpu_engine):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    world, B, S, H, D, seed, rs = (int(x) for x in z["meta"])
+    div = z["dividers"].tolist()
+    cu = z["cu"].tolist() if "cu" in z.files else None
+    data = O.drifting_qkv(B, S, H, D, len(div), seed=seed, drift=float(z["drift"]))
+    _init_schedule(world, div)
+    cpu_engine.OP_LOG = {}
+    try:
+        res = _ring_on_loopback(world, data, torch.device("cpu"), cu=cu,
+                                layer_setup=lambda layer: setattr(layer, "chain_launches", True))
+        log = cpu_engine.OP_LOG
+    finally:
+        cpu_engine.OP_LOG = None
+    gold = z["out"]
+    for r in range(world):
+        for t in range(len(div)):
+            mine = res[r][0][t]
+            if cu is not None:
+                valid = cu[r][1]
+                err = (mine[:, :valid] - torch.from_numpy(gold[t, r])[:, :valid]).abs().max().item()
+            else:
+                err = (mine[:, ::rs] - torch.from_numpy(gold[t, r])).abs().max().item()
+            assert err <= 2e-5, (name, r, t, err)
+    overlapped = _check_overlap_contract(log)
+    assert overlapped == sum(res[r][2]["overlapped_launches"] for r in range(world))
+    if world >= 4:
+        assert overlapped > 0          # a full refresh on four or more ranks has at least two foreign chunks in a row
+    else:
+        assert overlapped == 0         # two ranks: the one foreign chunk follows the wait for it
+
+
+def test_chained_launches_with_pair_map_keep_the_overlap_contract(cpu_engine):
+    world, T = 4, 5
+    reusable = np.random.RandomState(5).rand(T, world, world) < 0.5
+    reusable[0] = False
+    data = O.drifting_qkv(1, 64 * world, 2, 32, T, seed=9, drift=0.05)
+    _init_schedule(world, steps=T, pair_map=reusable)
+    cpu_engine.OP_LOG = {}
+    try:
+        res = _ring_on_loopback(world, data, torch.device("cpu"),
+                                layer_setup=lambda layer: setattr(layer, "chain_launches", True))
+        log = cpu_engine.OP_LOG
+    finally:
+        cpu_engine.OP_LOG = None
+    want = O.run_pair_map_group(world, reusable, data)
+    for r in range(world):
+        for t in range(T):
+            assert (res[r][0][t] - want[t][r]).abs().max() <= 2e-5
+    assert _check_overlap_contract(log) > 0
+
+
 def test_a_failing_rank_ends_the_others():
     def body(r, group, fabric):
         if r == 1:
@@ -197,6 +262,86 @@ def test_packed_ring_reuse_on_one_gpu():
         for t in range(len(div)):
             e = (res[r][0][t][0, :valid] - ref[t][r][:valid]).abs()
             assert e.max() <= 2e-2 and e.mean() <= 1e-3, (r, t, e.max().item(), e.mean().item())
+    assert ops.read_status() == 0
+
+
+@gpu
+@pytest.mark.parametrize("name", ["trace_n4", "batch2_n4", "n8", "n4_d64"])
+def test_chained_launches_on_one_gpu_equal_separate_launches_bit_for_bit(name):
+    """Launches that overlap the end of the one before them (the own chunk first, all waits, then the foreign
+    chunks back to back) do the same arithmetic in the same order: the results must equal those of the plain
+    sequence bit for bit, and both must match the oracle."""
+    from ditango_b200 import ops
+    c = RING_CASES[name]
+    world, div = c["world"], c["dividers"]
+    data = O.drifting_qkv(c["B"], c["S"], c["H"], c["D"], len(div), seed=c["seed"], drift=c["drift"], dtype=torch.bfloat16)
+    _init_schedule(world, div)
+    plain = _ring_on_loopback(world, data, torch.device("cuda"))
+    _init_schedule(world, div)
+    chained = _ring_on_loopback(world, data, torch.device("cuda"),
+                                layer_setup=lambda layer: setattr(layer, "chain_launches", True))
+    ref, _ = O.run_ring_group(world, div, data)
+    _check(chained, ref, world, len(div))
+    for r in range(world):
+        assert torch.equal(chained[r][0], plain[r][0]) and torch.equal(chained[r][1], plain[r][1]), r
+        assert plain[r][2]["overlapped_launches"] == 0
+    assert sum(chained[r][2]["overlapped_launches"] for r in range(world)) > 0
+    assert ops.read_status() == 0
+
+
+@gpu
+def test_chained_packed_ring_and_pair_map_on_one_gpu():
+    from ditango_b200 import ops
+    chain = lambda layer: setattr(layer, "chain_launches", True)  # noqa: E731
+    world, div = 4, [1, 1, 2, 2, 1]
+    S, H, D = 1040, 2, 128
+    lo = S // world
+    cu = [[0, lo - 17, lo], [0, lo - 31, lo], [0, lo, lo], [0, lo - 5, lo]]
+    data = O.drifting_qkv(1, S, H, D, len(div), seed=4, drift=0.05, dtype=torch.bfloat16)
+    _init_schedule(world, div)
+    res = _ring_on_loopback(world, data, torch.device("cuda"), cu=cu, layer_setup=chain)
+    ref, _ = O.run_ring_group(world, div, data, cu_per_rank=cu)
+    for r in range(world):
+        valid = cu[r][1]
+        for t in range(len(div)):
+            e = (res[r][0][t][0, :valid] - ref[t][r][:valid]).abs()
+            assert e.max() <= 2e-2 and e.mean() <= 1e-3, (r, t, e.max().item(), e.mean().item())
+    world, T = 8, 6
+    reusable = np.random.RandomState(3).rand(T, world, world) < 0.6
+    reusable[0] = False
+    data = O.drifting_qkv(2, 150 * world, 2, 64, T, seed=6, drift=0.05, dtype=torch.bfloat16)
+    _init_schedule(world, steps=T, pair_map=reusable)
+    res = _ring_on_loopback(world, data, torch.device("cuda"), layer_setup=chain)
+    _check(res, O.run_pair_map_group(world, reusable, data), world, T)
+    assert sum(res[r][2]["overlapped_launches"] for r in range(world)) > 0
+    assert ops.read_status() == 0
+
+
+@gpu
+@pytest.mark.parametrize("D,H", [(128, 8), (64, 16)])
+def test_overlapping_launches_accumulate_like_separate_ones(D, H):
+    """Seven chunks folded into one state by seven launches, each several waves long with a partly filled last
+    wave (so a launch really starts while the one before it is finishing): with and without overlap the state
+    must be the same bit for bit, and equal the state of one launch over all keys within rounding."""
+    from ditango_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(11)
+    Sq, Sk, n = 5000, 1500, 7
+    q = torch.randn(1, Sq, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    ks = [torch.randn(1, Sk, H, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(n)]
+    vs = [torch.randn(1, Sk, H, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(n)]
+
+    def fold(overlap):
+        out, lse = ops.flash_partial(q, ks[0], vs[0], lse_layout=ops.LSE_BSH)
+        for i in range(1, n):
+            ops.flash_partial(q, ks[i], vs[i], out=out, lse=lse, accumulate=True, lse_layout=ops.LSE_BSH,
+                              overlap_previous=overlap)
+        return out, lse
+    a = fold(False)
+    b = fold(True)
+    torch.cuda.synchronize()
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    whole = ops.flash_partial(q, torch.cat(ks, 1), torch.cat(vs, 1), lse_layout=ops.LSE_BSH)
+    assert (whole[0] - b[0]).abs().max() <= 2e-2 and (whole[1] - b[1]).abs().max() <= 1e-3
     assert ops.read_status() == 0
 
 
@@ -443,8 +588,9 @@ def test_dit_with_reuse_schedule_on_one_gpu_stays_close_to_full_refresh():
 
 
 # ------------------------------------------------------------------------------------------ copy-engine transport (CPU half)
+@pytest.mark.parametrize("chain", [False, True])
 @pytest.mark.parametrize("name", ["cfg1_n2", "trace_n4", "n8", "varlen_n4"])
-def test_peer_copy_transport_protocol_reproduces_executed_reference(name, cpu_engine):
+def test_peer_copy_transport_protocol_reproduces_executed_reference(name, chain, cpu_engine):
     """The request / push / ready protocol of core/peer_transport.py (sequence numbers, alternating buffers,
     slots shared by all sources) under the attention objects, on threads with in-process stand-ins for device
     memory and events: the outputs are still those of the executed reference."""
@@ -458,6 +604,7 @@ def test_peer_copy_transport_protocol_reproduces_executed_reference(name, cpu_en
 
     def body(r, group, fabric):
         layer = proAttention(0, LB.thread_peer_group(group))
+        layer.chain_launches = chain          # chained: all hops of a call are waited for before the foreign chunks
         outs = []
         for t, (q, k, v) in enumerate(data):
             LB.stepped(fabric, r, t)
