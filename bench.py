@@ -275,7 +275,7 @@ def run_ours(args):
         rm._refine_divider_map()
         rm.screen_self_sends()
     proAttention.hop_grouping = args.hop_grouping
-    proAttention.chain_launches = bool(args.chain)
+    proAttention.chain_launches = {"auto": "auto", "on": True, "off": False}[args.chain]
     layers = [proAttention(l, group) for l in range(w["layers"])]
     raw, gen = make_inputs(w, rank, world, device)
     B, H, D, S = w["B"], w["H"], w["D"], w["S"]
@@ -334,6 +334,7 @@ def run_ours(args):
         rx_timed = int(4 * (world - 1) / world * B * S_loc * H * D * 2) * w["layers"] * args.steps
     clocks = sampler.stop() if rank == 0 else None
     launches = ops.LaunchLog.count
+    overlapped_here = ops.LaunchLog.overlapped
     flash_ms = [a.elapsed_time(b) for a, b, _ in ops.LaunchLog.events]
     flash_flops = [f for _, _, f in ops.LaunchLog.events]
     exposed_ms = sum(L.exposed_comm_ms() for L in layers)
@@ -472,7 +473,7 @@ def run_ours(args):
     # ---------------------------------------------------------------- reduce over ranks
     stats = torch.tensor([elapsed_ms, e2e_ms, exposed_ms, copy_ms] + (plain if plain is not None else [0.0, 0.0]),
                          device=device, dtype=torch.float64)
-    sums = torch.tensor([sum(flash_flops), e2e_flops, sum(flash_ms), float(len(flash_ms)), float(launches)],
+    sums = torch.tensor([sum(flash_flops), e2e_flops, sum(flash_ms), float(len(flash_ms)), float(launches), float(overlapped_here)],
                         device=device, dtype=torch.float64)
     # whole-path roofline of this rank's timed steps: the slower of its MMA work at the measured bf16 peak
     # and its received KV bytes at the measured peer-copy bandwidth (770 GB/s per direction on this pool)
@@ -485,7 +486,7 @@ def run_ours(args):
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
         dist.all_reduce(roof, op=dist.ReduceOp.MAX)
     elapsed_ms, e2e_ms, exposed_ms, copy_ms, plain_ms, plain_exposed_ms = stats.tolist()
-    tot_flops, tot_e2e_flops, tot_flash_ms, n_flash, tot_launches = sums.tolist()
+    tot_flops, tot_e2e_flops, tot_flash_ms, n_flash, tot_launches, overlapped = sums.tolist()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -508,7 +509,7 @@ def run_ours(args):
                        "schedule": args.schedule if (args.mode == "ditango" and world > 1) else "none",
                        "hop_grouping": args.hop_grouping if (args.mode != "ulysses" and world > 1) else "none",
                        "transport": args.transport if (args.mode != "ulysses" and world > 1) else "none",
-                       "chain_launches": bool(args.chain and args.mode != "ulysses" and world > 1)},
+                       "chain_launches": args.chain if (args.mode != "ulysses" and world > 1) else "none"},
             "algorithmic_tflops_full_attention": round(full_flops / (elapsed_ms * 1e-3) / 1e12, 2),
             "exposed_comm_ms_per_step": round(exposed_ms / args.steps, 3),
             "pct_of_bf16_peak": round(100.0 * value / world / peaks["tensor_burst"], 2),
@@ -517,8 +518,8 @@ def run_ours(args):
                          "peak_kind": f"{peaks['source']} sustained bf16 cuBLAS GEMM; burst {peaks['tensor_burst']}",
                          "kernel": f"flash_fwd_row_kernel<{D}>" if D == 128 else f"flash_fwd_pair_kernel<{D}>",
                          "launches_timed": int(n_flash),
-                         "timed_unit": ("one launch, or one chain of overlapping launches (FLOPs of the chain over its "
-                                        "duration)") if (args.chain and world > 1) else "one launch",
+                         "timed_unit": "one launch (a launch that overlaps the one before it: from that launch's end to its own)",
+                         "overlapped_launches": int(overlapped),
                          "traffic": round(flash_dram_traffic(B, S_loc, H, D)),
                          "traffic_kind": "bytes per launch, scaled by tensor size from the ncu capture of a smaller chunk pair"},
             "clocks": clocks,
@@ -728,7 +729,7 @@ def run_dit(args):
         rm.screen_self_sends()
     torch.manual_seed(0)
     proAttention.hop_grouping = args.hop_grouping
-    proAttention.chain_launches = bool(args.chain)
+    proAttention.chain_launches = {"auto": "auto", "on": True, "off": False}[args.chain]
     with torch.device(device):
         model = CogVideoXDiT(dcfg, group, mode=args.mode).to(torch.bfloat16)
     g = torch.Generator(device=device).manual_seed(0)
@@ -811,27 +812,42 @@ def run_micro(args):
         out = torch.empty(B, S, H, D, device=dev, dtype=torch.float32)
         lse = torch.empty(B, S, H, device=dev, dtype=torch.float32)
 
-        def chain(overlap):
+        # An event recorded long ago on another stream: waiting for it between two launches is what a transport's
+        # "chunk has arrived" wait looks like to the compute stream when the chunk is already there.
+        side = torch.cuda.Stream()
+        landed = torch.cuda.Event()
+        with torch.cuda.stream(side):
+            landed.record()
+        side.synchronize()
+        cur = torch.cuda.current_stream()
+
+        def chain(overlap, between=None):
             ops.flash_partial(q, kv[0][0], kv[0][1], out=out, lse=lse, lse_layout=ops.LSE_BSH)
             for kk, vv in kv[1:]:
+                if between == "wait":
+                    cur.wait_event(landed)
+                elif between == "record":
+                    torch.cuda.Event().record()
                 ops.flash_partial(q, kk, vv, out=out, lse=lse, accumulate=True, lse_layout=ops.LSE_BSH,
                                   overlap_previous=overlap)
-        res = {}
-        for overlap in (False, True):
+        res, ref, same = {}, None, True
+        for name, overlap, between in (("separate", False, None), ("overlapped", True, None),
+                                       ("overlapped_event_wait_between", True, "wait"),
+                                       ("overlapped_event_record_between", True, "record")):
             for _ in range(max(1, args.warmup)):
-                chain(overlap)
+                chain(overlap, between)
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for _ in range(max(1, args.steps)):
-                chain(overlap)
+                chain(overlap, between)
             b.record()
             torch.cuda.synchronize()
             ms = a.elapsed_time(b) / max(1, args.steps)
-            res["overlapped" if overlap else "separate"] = {
-                "ms": round(ms, 4), "tflops": round(4.0 * B * H * S * S * D * n / (ms * 1e-3) / 1e12, 1)}
-            ref = (out.clone(), lse.clone()) if not overlap else ref
-        same = bool(torch.equal(ref[0], out) and torch.equal(ref[1], lse))
+            res[name] = {"ms": round(ms, 4), "tflops": round(4.0 * B * H * S * S * D * n / (ms * 1e-3) / 1e12, 1)}
+            if ref is None:
+                ref = (out.clone(), lse.clone())
+            same = same and bool(torch.equal(ref[0], out) and torch.equal(ref[1], lse))
         print(json.dumps({"micro": "chain", "workload": args.workload, "shape": dict(B=B, S=S, H=H, D=D), "launches": n,
                           **res, "speedup": round(res["separate"]["ms"] / res["overlapped"]["ms"], 4),
                           "bit_identical": same, "peak_burst": peaks["tensor_burst"], "status": ops.read_status()}), flush=True)
@@ -888,9 +904,9 @@ def main():
     ap.add_argument("--transport", default="peer", choices=["nccl", "peer"],
                     help="KV hops by copy-engine copies into IPC-mapped buffers of the consumer (default: no SM is taken "
                          "from the attention kernel, full link rate per pair), or by NCCL send/receive")
-    ap.add_argument("--chain", action="store_true",
-                    help="ditango / ring mode at N > 1: own chunk first, wait for all incoming chunks, then the remaining "
-                         "attention launches back to back, each overlapping the end of the one before it")
+    ap.add_argument("--chain", default="auto", choices=["auto", "on", "off"],
+                    help="attention launches of one layer call that overlap the end of the launch before them "
+                         "(proAttention.chain_launches): auto = launches below 5e11 FLOP, on = all, off = none")
     ap.add_argument("--cpu-seq", type=int, default=4096, help="tokens per rank of the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the parity miniature that runs before the warm-up at N > 1")

@@ -76,14 +76,21 @@ class proAttention:
     # dtype of the values of cached block states (the reference keeps fp32: utils.py:76); bfloat16 halves
     # the cache's footprint and read traffic.  lse stays fp32.
     cache_dtype = torch.float32
-    # Overlapping attention launches.  The chunks of a call are attended by one launch each, and a launch's
-    # grid rarely divides evenly over the SMs, so each ends in a partly filled wave.  With True the own chunk
-    # is attended first, then ALL incoming chunks of the call are waited for, then the remaining launches are
-    # queued back to back with nothing between them on the stream, each allowed to start while the one
-    # before it is finishing (ops.flash_partial(overlap_previous=True)).  The price: no chunk is attended
-    # before the last one has arrived, so it pays where transfers are short against the own chunk's launch.
-    # Every rank of a group must agree.
-    chain_launches = False
+    # Overlapping attention launches.  The chunks of a call are attended by one launch each; every launch ends
+    # in a partly filled wave and is followed by a launch gap.  A launch made with overlap_previous starts while
+    # the attention launch before it is finishing (ops.flash_partial); that is allowed when only event waits /
+    # records were queued on the stream since that launch.
+    #   "auto"  overlap where it was measured to pay: launches of less than OVERLAP_MAX_FLOPS (short ones, where
+    #           gap and tail are a visible share; long D = 128 launches run at the board's power cap, where the
+    #           idle tail is what lets the clock recover, and lose about 1 %), and only on transports whose wait
+    #           for an incoming chunk is an event wait (the group says so: `wait_is_event_only`);
+    #   True    overlap every launch that may.  On a transport that copies on the compute stream when it waits,
+    #           the own chunk is attended first, then ALL incoming chunks are waited for, then the remaining
+    #           launches go back to back;
+    #   False   never.
+    # Every rank of a group must agree.  Results are bit-identical in all three.
+    chain_launches = "auto"
+    OVERLAP_MAX_FLOPS = 5.0e11
 
     def __init__(self, layer_id: int, isp_group):
         self.group = isp_group
@@ -187,7 +194,8 @@ class proAttention:
     def _wait_hop(self, handle):
         if handle is None:          # covered by the batch of an earlier hop
             return
-        self._chain_open = False    # a wait (or the transport's copy) now sits behind the last launch
+        if not getattr(self.group, "wait_is_event_only", False):
+            self._chain_open = False    # the transport's copy now sits behind the last launch
         if self.measure_comm and torch.cuda.is_available():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -197,22 +205,25 @@ class proAttention:
         else:
             self.group.p2p_wait_batch(handle)
 
+    def _chain_mode(self) -> Tuple[bool, bool]:
+        """(launches may overlap, own chunk first and all waits before the other launches)."""
+        mode = self.chain_launches
+        event_only = bool(getattr(self.group, "wait_is_event_only", False))
+        if mode == "auto":
+            return event_only, False
+        return bool(mode), bool(mode) and not event_only
+
     def _attend(self, chain: bool, query, kk, vv, **kw):
-        """One attention launch; in chain mode it overlaps the previous one when that was an attention launch
-        of this object with nothing queued on the stream since."""
-        if chain and self._chain_open:
+        """One attention launch; with `chain` it overlaps the previous one when that was an attention launch of
+        this object and no kernel or copy was queued on the stream since."""
+        if chain and self._chain_open and (self.chain_launches != "auto" or
+                                           4.0 * query.numel() * kk.shape[-3] < self.OVERLAP_MAX_FLOPS):
             kw["overlap_previous"] = True
         self.stats["chunks_attended"] += 1
         self.stats["overlapped_launches"] += int("overlap_previous" in kw)
         res = _engine.flash_partial(query, kk, vv, lse_layout=LSE_BSH, **kw)
         self._chain_open = True
         return res
-
-    @staticmethod
-    def _chain_timing(begin: bool):
-        log = getattr(_engine, "LaunchLog", None)
-        if log is not None:
-            (log.chain_begin if begin else log.chain_end)()
 
     def exposed_comm_ms(self, reset: bool = True) -> float:
         """Time the compute stream spent blocked on incoming KV since the last reset."""
@@ -232,7 +243,7 @@ class proAttention:
         packed = cu_q is not None
         payload = (key, value, cu_kv) if packed else (key, value)
 
-        chain = bool(self.chain_launches)
+        chain, reorder = self._chain_mode()
         self._chain_open = False
 
         def attend(kv, keep=False):
@@ -244,18 +255,15 @@ class proAttention:
         plan = plan_pair_step(N, flags, self._have)
         posted = self._post_hops(plan, plan.n_hops, payload)
         own = attend(payload)
-        if chain:
+        if reorder:
             for hop in range(plan.n_hops):
                 self._wait_hop(posted[hop][1])
-            self._chain_timing(True)
         for hop in range(plan.n_hops):
             current, handle = posted[hop]
-            if not chain:
+            if not reorder:
                 self._wait_hop(handle)
             if current is not None:
                 self._chunk_states[plan.ranks[me].owners[hop]] = attend(current, keep=True)
-        if chain:
-            self._chain_timing(False)
         self._chain_open = False
         others = [(o, l, LSE_BSH) for src in ((me + i) % N for i in range(1, N))
                   for o, l in (self._chunk_states.get(src, (None, None)),) if l is not None]
@@ -300,7 +308,8 @@ class proAttention:
         keep_chunks = stride == N and next_stride != N        # fine-grained store after a full refresh
         keep_block = stride != N and next_stride != N
 
-        chain = bool(self.chain_launches) and N > 1
+        chain, reorder = self._chain_mode()
+        chain, reorder = chain and N > 1, reorder and N > 1
         self._chain_open = False
 
         def attend(kv, into=None, dtype=torch.float32):
@@ -328,14 +337,13 @@ class proAttention:
         # A single rank with nothing to merge gets its bf16 result straight from the attention kernel.
         direct16 = N == 1 and self.output_dtype == torch.bfloat16 and not rmap.is_auto_setting()
         own = None
-        if mine.own_first or chain:
-            # target block is a foreign one: own chunk first, overlapping hop 0.  Chained launches: always first,
+        if mine.own_first or reorder:
+            # target block is a foreign one: own chunk first, overlapping hop 0.  Reordered launches: always first,
             # so that the transfers run under it and every wait sits in front of the launches that overlap.
             own = attend(payload)
-        if chain:
+        if reorder:
             for hop in range(stride):
                 self._wait_hop(posted[hop][1])
-            self._chain_timing(True)
 
         # 3. the target block's chunks.  A state that goes to the cache without further accumulation is
         #    written by the attention kernel in the cache's dtype: no cast pass afterwards.
@@ -344,10 +352,10 @@ class proAttention:
         fresh_chunks = sum(1 for o in mine.owners if o != me)
         for hop in range(stride):
             current, handle = posted[hop]
-            if not chain:
+            if not reorder:
                 self._wait_hop(handle)
             if mine.owners[hop] == me:
-                if own is None:            # (chained launches attended it before the waits)
+                if own is None:            # (reordered launches attended it before the waits)
                     own = attend(payload, dtype=torch.bfloat16 if direct16 else torch.float32)
             elif keep_chunks:
                 st = attend(current, dtype=self.cache_dtype)
@@ -360,8 +368,6 @@ class proAttention:
             else:
                 own = attend(current, into=own)          # nothing is kept: fold into the result
 
-        if chain:
-            self._chain_timing(False)
         self._chain_open = False
 
         # 4. store the fresh block, combine everything in one pass

@@ -10,6 +10,10 @@ import torch.distributed as dist
 
 
 class GroupCoordinator:
+    # p2p_wait_batch only makes the current stream wait for events (torch's Work.wait on NCCL requests): no kernel
+    # or copy of the transport is queued between the caller's own launches.  proAttention reads this.
+    wait_is_event_only = True
+
     def __init__(self, group_ranks: List[List[int]], local_rank: int, torch_distributed_backend: str,
                  group_name: Optional[str] = None):
         self.unique_name = group_name or "anonymous"

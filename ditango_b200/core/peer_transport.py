@@ -71,6 +71,8 @@ class _Remote:
 
 class PeerCopyGroup:
     MAX_CHANNELS = 256
+    # p2p_wait_batch queues nothing but event waits on the caller's stream (the copies run on the owner's copy stream)
+    wait_is_event_only = True
 
     def __init__(self, group, timeout_s: float = 120.0):
         self.inner = group

@@ -16,38 +16,19 @@ from ._capi import DTB_BF16, DTB_F32, LSE_BHS, LSE_BSH
 class LaunchLog:
     """Optional accounting of kernel launches made through this module.  `count` always runs; with
     `events` enabled every flash launch is bracketed by two CUDA events on the launching stream so
-    a benchmark can read per-launch device time and the FLOPs each launch executed."""
+    a benchmark can read per-launch device time and the FLOPs each launch executed.  (An event between two
+    launches does not keep the second from overlapping the first; for a launch that overlaps its predecessor the
+    pair then reads "end of the previous launch to end of this one", so the durations of a chain still add up to
+    the chain's time.)"""
     count = 0
     events = None            # list of (start_event, end_event, flops) while enabled
     overlapped = 0           # flash launches made with overlap_previous
-    _chain = None            # [start_event, flops] while a chain of overlapping launches is being timed as one
 
     @classmethod
     def reset(cls, with_events: bool = False):
         cls.count = 0
         cls.overlapped = 0
         cls.events = [] if with_events else None
-        cls._chain = None
-
-    @classmethod
-    def chain_begin(cls):
-        """Launches that overlap one another cannot be timed one by one (an event between two of them would
-        also sit between the kernels on the stream): from here to chain_end() the flash launches are timed
-        as ONE entry of `events`, with their FLOPs added up."""
-        if cls.events is not None and cls._chain is None:
-            start = torch.cuda.Event(enable_timing=True)
-            start.record()
-            cls._chain = [start, 0.0]
-
-    @classmethod
-    def chain_end(cls):
-        if cls._chain is not None:
-            start, flops = cls._chain
-            cls._chain = None
-            if flops > 0:
-                end = torch.cuda.Event(enable_timing=True)
-                end.record()
-                cls.events.append((start, end, flops))
 
 
 def _stream_ptr() -> int:
@@ -127,9 +108,10 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     (out, lse) in place.  lse is [B,H,Sq] / [H,Tq] (LSE_BHS) or [B,Sq,H] / [Tq,H] (LSE_BSH).
 
     overlap_previous=True lets the launch start while the launch queued just before it on the current stream
-    is finishing (DTB_LAUNCH_OVERLAP_PREVIOUS).  Only pass it when that operation was another flash_partial
-    call and nothing else -- no copy, event wait or other kernel -- was queued on the stream since, and when
-    q, k, v, cu_seqlens were not written by that call; (out, lse) may be the state that call wrote.
+    is finishing (DTB_LAUNCH_OVERLAP_PREVIOUS).  Only pass it when the last kernel or copy queued on the
+    stream was another flash_partial call -- event waits and event records in between are fine, they neither
+    write memory nor keep the launches from overlapping -- and when q, k, v, cu_seqlens were not written by
+    that call; (out, lse) may be the state that call wrote.
     """
     lib = _capi.load()
     _need_cuda(q, k, v, out, lse, cu_seqlens_q, cu_seqlens_k)
@@ -172,11 +154,7 @@ def flash_partial(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     # dense: every query row meets every key row of its sequence; packed: upper bound by maxima
     flops = 4.0 * nseg * H * sq * sk * D
     ev = None
-    if LaunchLog._chain is not None:
-        LaunchLog._chain[1] += flops
-    elif LaunchLog.events is not None:
-        if overlap_previous:
-            raise _capi.ExtensionError("per-launch timing needs LaunchLog.chain_begin() around overlapping launches")
+    if LaunchLog.events is not None:
         ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         ev[0].record()
     rc = lib.dtb_flash_fwd_ex(

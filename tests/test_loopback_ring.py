@@ -588,7 +588,7 @@ def test_dit_with_reuse_schedule_on_one_gpu_stays_close_to_full_refresh():
 
 
 # ------------------------------------------------------------------------------------------ copy-engine transport (CPU half)
-@pytest.mark.parametrize("chain", [False, True])
+@pytest.mark.parametrize("chain", [False, True, "auto"])
 @pytest.mark.parametrize("name", ["cfg1_n2", "trace_n4", "n8", "varlen_n4"])
 def test_peer_copy_transport_protocol_reproduces_executed_reference(name, chain, cpu_engine):
     """The request / push / ready protocol of core/peer_transport.py (sequence numbers, alternating buffers,
@@ -604,7 +604,7 @@ def test_peer_copy_transport_protocol_reproduces_executed_reference(name, chain,
 
     def body(r, group, fabric):
         layer = proAttention(0, LB.thread_peer_group(group))
-        layer.chain_launches = chain          # chained: all hops of a call are waited for before the foreign chunks
+        layer.chain_launches = chain          # this transport's waits are event waits: launches overlap through them
         outs = []
         for t, (q, k, v) in enumerate(data):
             LB.stepped(fabric, r, t)
@@ -622,6 +622,7 @@ def test_peer_copy_transport_protocol_reproduces_executed_reference(name, chain,
     gold = z["out"]
     for r in range(world):
         assert res[r][1]["chunks_received"] > 0
+        assert (res[r][1]["overlapped_launches"] > 0) == bool(chain)      # (the cases are far below the size limit of "auto")
         for t in range(len(div)):
             mine = res[r][0][t]
             if cu is not None:
@@ -630,6 +631,27 @@ def test_peer_copy_transport_protocol_reproduces_executed_reference(name, chain,
             else:
                 err = (mine[:, ::rs] - torch.from_numpy(gold[t, r])).abs().max().item()
             assert err <= 2e-5, (name, r, t, err)
+
+
+def test_overlap_rule_of_the_automatic_mode():
+    """"auto" overlaps only short launches, and only on transports whose wait is an event wait."""
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.group_coordinate import SingleRankGroup
+
+    class G(SingleRankGroup):
+        wait_is_event_only = True
+    layer = proAttention(0, G(torch.device("cpu")))
+    assert layer.chain_launches == "auto" and layer._chain_mode() == (True, False)
+    layer.chain_launches = True
+    assert layer._chain_mode() == (True, False)
+    layer.chain_launches = False
+    assert layer._chain_mode() == (False, False)
+    plain = proAttention(0, SingleRankGroup(torch.device("cpu")))
+    assert plain._chain_mode() == (False, False)
+    plain.chain_launches = True
+    assert plain._chain_mode() == (True, True)         # copies on the stream when it waits: own chunk first, all waits, then the rest
+    # size rule: CogVideoX chunk at 8 ranks is below the limit, HunyuanVideo's is above
+    assert 4.0 * (2 * 2222 * 48 * 64) * 2222 < proAttention.OVERLAP_MAX_FLOPS < 4.0 * (14882 * 24 * 128) * 14882
 
 
 def test_peer_copy_transport_with_pair_map(cpu_engine):
