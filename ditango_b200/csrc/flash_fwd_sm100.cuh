@@ -28,8 +28,9 @@ struct FlashParams {
 
 // With p.overlap_previous the launch may begin while the previous launch on `stream` is finishing (its CTAs fill
 // the SMs that kernel's last wave leaves idle).  The kernels read q, k, v, cu_seqlens before they wait for that
-// kernel and touch (out, lse) only after it has completed, so this is allowed exactly when the previous operation
-// on the stream is another launch_flash whose results this launch does not read as q, k, v or cu_seqlens.
+// kernel and touch (out, lse) only after it has completed, so this is allowed exactly when the last kernel or copy
+// queued on the stream is another launch_flash whose results this launch does not read as q, k, v or cu_seqlens
+// (event waits and records in between do not matter).
 template <int D>
 cudaError_t launch_flash(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v,
                          const FlashParams& p, cudaStream_t stream);

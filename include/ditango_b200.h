@@ -139,10 +139,11 @@ DTB_API int dtb_flash_fwd(const void* q, const void* k, const void* v,
  *      is finishing: its CTAs take the SMs that launch's last wave leaves idle (programmatic dependent
  *      launch).  The kernel reads q, k, v and cu_seqlens at once, and waits for the previous launch to
  *      complete before it reads or writes (out, lse) -- so accumulating into the state the previous launch
- *      wrote is fine.  Contract: the operation queued just before this call on `stream` must be another
+ *      wrote is fine.  Contract: the last kernel or copy queued on `stream` before this call must be another
  *      dtb_flash_fwd / dtb_flash_fwd_ex launch, and this call's q, k, v, cu_seqlens must not be produced by
- *      it.  With anything else in between (a copy, an event wait, another kernel) pass 0: inputs written
- *      by the operation just before are only guaranteed visible to a launch without the flag.
+ *      it.  Event waits and event records in between are fine (they write no memory and do not stop the
+ *      overlap).  After any other kernel or a copy pass 0: what the operation just before wrote is only
+ *      guaranteed visible to a launch without the flag.
  */
 #define DTB_LAUNCH_OVERLAP_PREVIOUS 1
 DTB_API int dtb_flash_fwd_ex(const void* q, const void* k, const void* v,
