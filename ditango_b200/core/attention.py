@@ -25,7 +25,7 @@ import torch
 import torch.distributed
 
 from .. import ops as _engine
-from .._capi import LSE_BHS, LSE_BSH
+from .._capi import LSE_BSH
 from ..logger import init_logger
 from ..timer import get_timer
 from ..utils import get_timestep

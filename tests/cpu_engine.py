@@ -1,7 +1,6 @@
 """CPU stand-in for ditango_b200.ops, built on the oracle's arithmetic.  TEST-ONLY: the host-side
 control plane (schedule, cache, transport order) is exercised on gloo ranks without a GPU by
 swapping this in for the kernel wrappers.  The product package never imports it."""
-import math
 
 import torch
 

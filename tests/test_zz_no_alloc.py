@@ -8,7 +8,6 @@ consecutive calls (the built-in array is shared and keeps its old contents), and
 than the array covers.  This file is collected last so that a run stopping at the first failure has
 already exercised everything else.
 """
-import ctypes
 
 import pytest
 import torch
