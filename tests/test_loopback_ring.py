@@ -696,3 +696,36 @@ def test_peer_copy_transport_gives_up_on_a_silent_peer(cpu_engine):
             return "timed out"
         return "silent"
     assert LB.run_ranks(2, body) == ["timed out", "silent"]
+
+
+def test_peer_copy_transport_when_a_rank_leaves_between_steps(cpu_engine):
+    """Four ranks run full-refresh steps; rank 3 stops after step 1 (between steps, nothing of its own in
+    flight).  The others' next call must end with TransportTimeout after the bounded host wait -- as owners waiting
+    for rank 3's request or as consumers waiting for its chunk -- not hang."""
+    import time
+    from ditango_b200.core.attention import proAttention
+    from ditango_b200.core.peer_transport import TransportTimeout
+    from ditango_b200.utils import update_timestep
+    world, T = 4, 3
+    _init_schedule(world, [1] * T)
+    data = O.drifting_qkv(1, 32 * world, 2, 32, T, seed=1, drift=0.0)
+    update_timestep(0)          # every row of the schedule is the same: the step index needs no hand-shake here
+
+    def body(r, group, fabric):
+        layer = proAttention(0, LB.thread_peer_group(group, timeout_s=1.5))
+        done = 0
+        for t, (q, k, v) in enumerate(data):
+            if r == 3 and t == 2:
+                return ("left", done)
+            lo, hi = r * q.shape[1] // world, (r + 1) * q.shape[1] // world
+            t0 = time.time()
+            try:
+                layer.attn(*(x[:, lo:hi].contiguous() for x in (q, k, v)))
+            except TransportTimeout:
+                return ("gave up", done, time.time() - t0)
+            done += 1
+        return ("finished", done)
+    res = LB.run_ranks(world, body, timeout_s=30.0)
+    assert res[3] == ("left", 2)
+    for r in range(3):
+        assert res[r][0] == "gave up" and res[r][1] == 2 and res[r][2] < 10.0, res[r]
