@@ -68,6 +68,49 @@ def test_planner_matches_pointer_replay(world, div):
         assert ptr == tr[t]["pointer_after"]
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_planner_on_random_legal_schedules(world):
+    """Sixty random schedules per group size, drawn like the benchmark's (Bernoulli reuse, a random legal divider),
+    legalised and screened by the package's own RedundancyMap: at every step the planner's target blocks, first-KV
+    sources and pointers equal the integer replay of the reference's state machine, every hop is a partial
+    permutation, and every rank attends each chunk of its target block exactly once."""
+    from ditango_b200.core.schedule import plan_step
+    rng = np.random.RandomState(100 + world)
+    legal = [d for d in (2, 4, 8) if d <= world]
+    for case in range(60):
+        T = int(rng.randint(4, 14))
+        div = np.ones((T, 1), dtype=np.int64)
+        for t in range(1, T):
+            if rng.rand() < 0.65:
+                div[t, 0] = legal[rng.randint(len(legal))]
+        rm = _rm(T, 1, world)
+        rm.divider_map = torch.from_numpy(div)
+        rm._refine_divider_map()
+        rm.screen_self_sends()
+        col = [int(x) for x in rm.get_map()[:, 0].tolist()]
+        tr = O.replay_pointers(col, world)
+        ptr = [0] * world
+        dm = np.asarray(col).reshape(-1, 1)
+        for t in range(T):
+            s = O.stride_now(dm, world, t, 0)
+            plan = plan_step(world, s, ptr)
+            assert [p.target_block for p in plan.ranks] == tr[t]["target_block"], (case, col, t)
+            assert not any(tr[t]["self_send"]), (case, col, t)
+            for r in range(world):
+                src = tr[t]["first_kv_from"][r]
+                assert plan.ranks[r].own_first == (src is not None)
+                tb = plan.ranks[r].target_block
+                want = set(range(tb * s, tb * s + s)) - ({r} if plan.ranks[r].own_first else set())
+                assert sorted(plan.ranks[r].owners) == sorted(want | ({r} if not plan.ranks[r].own_first else set())), (case, col, t, r)
+                for hop in range(s):
+                    assert len(plan.send_to(r, hop)) <= 1
+                    got = plan.recv_from(r, hop)
+                    if got is not None:
+                        assert r in plan.send_to(got, hop) and got == plan.ranks[r].owners[hop]
+            ptr = plan.pointers_after
+            assert ptr == tr[t]["pointer_after"], (case, col, t)
+
+
 def _rm(T, L, world):
     from ditango_b200.core.redundancy_map import RedundancyMap
 

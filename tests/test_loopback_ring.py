@@ -122,6 +122,32 @@ def test_loopback_collectives(cpu_engine):
         assert torch.equal(got, torch.full((3,), float((r - 1) % world)))
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_random_legal_schedules_match_the_oracle(world, cpu_engine):
+    """Host control plane on logical ranks against the oracle's state machine on random schedules (Bernoulli reuse,
+    random legal dividers, legalised and screened): fp32 arithmetic on both sides, so any difference in which
+    chunks are fetched, cached, merged or dropped shows as an error far above rounding."""
+    rng = np.random.RandomState(7 + world)
+    legal = [d for d in (2, 4, 8) if d <= world]
+    for case in range(3):
+        T = 9
+        div = np.ones((T, 1), dtype=np.int64)
+        for t in range(1, T):
+            if rng.rand() < 0.7:
+                div[t, 0] = legal[rng.randint(len(legal))]
+        rm = _init_schedule(world, [1] * T)
+        rm.divider_map = torch.from_numpy(div)
+        rm._refine_divider_map()
+        rm.screen_self_sends()
+        col = [int(x) for x in rm.get_map()[:, 0].tolist()]
+        data = O.drifting_qkv(1, 24 * world, 2, 32, T, seed=40 + case, drift=0.05)
+        res = _ring_on_loopback(world, data, torch.device("cpu"))
+        ref, _ = O.run_ring_group(world, col, data)
+        for r in range(world):
+            for t in range(T):
+                assert (res[r][0][t] - ref[t][r]).abs().max() <= 2e-5, (col, r, t)
+
+
 def _check_overlap_contract(log):
     """Every launch made with overlap_previous must directly follow another attention launch of the same rank:
     nothing else (a wait for incoming KV, a merge, a copy) may have been queued in between."""
