@@ -73,10 +73,15 @@ def _worker(rank, world, case, port, ret):
     g = torch.Generator().manual_seed(case.get("seed", 0) * 1000 + rank)
     dt = torch.bfloat16 if case.get("bf16", True) else torch.float32
     lo = S // world
-    q, k, v = (torch.randn(B, lo, H, D, generator=g) for _ in range(3))
+    data = case.get("data")          # optional: per step (q, k, v) of the WHOLE sequence, sliced here by rank
+    outs = [] if case.get("collect") else None
+    if data is None:
+        q, k, v = (torch.randn(B, lo, H, D, generator=g) for _ in range(3))
     seconds = 0.0
     for t in range(len(div)):
-        if t > 0:
+        if data is not None:
+            q, k, v = (x[:, rank * lo:(rank + 1) * lo].contiguous() for x in data[t])
+        elif t > 0:
             q, k, v = (x + case.get("drift", 0.05) * torch.randn(x.shape, generator=g) for x in (q, k, v))
         qq, kk = q, k
         if case.get("rms"):
@@ -86,10 +91,12 @@ def _worker(rank, world, case, port, ret):
         update_timestep(t)
         dist.barrier()
         t0 = time.perf_counter()
-        layer.attn(*args)
+        o = layer.attn(*args)
         dist.barrier()
         seconds += time.perf_counter() - t0
-    ret[rank] = (seconds, _FLOPS[0])
+        if outs is not None:
+            outs.append(o.float().numpy().copy())
+    ret[rank] = (seconds, _FLOPS[0], outs)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -97,7 +104,8 @@ def _worker(rank, world, case, port, ret):
 def time_reference(world, case, port=29790, limit_s=600.0):
     """Runs the reference's proAttention.attn for len(case['dividers']) steps of one layer on `world` gloo
     ranks (world >= 2: the reference has no attention group at one rank).  Returns
-    dict(seconds, flops, steps, cores)."""
+    dict(seconds, flops, steps, cores); with case["collect"] also the reference's outputs per rank and step
+    (case["data"], per step (q, k, v) of the whole sequence, then replaces the harness's own random inputs)."""
     assert world >= 2 and available()
     mgr = mp.Manager()
     ret = mgr.dict()
@@ -130,4 +138,7 @@ def time_reference(world, case, port=29790, limit_s=600.0):
                 os.environ[k] = v
     secs = max(ret[r][0] for r in range(world))
     flops = sum(ret[r][1] for r in range(world))
-    return dict(seconds=secs, flops=flops, steps=len(case["dividers"]), cores=os.cpu_count() or 1)
+    res = dict(seconds=secs, flops=flops, steps=len(case["dividers"]), cores=os.cpu_count() or 1)
+    if case.get("collect"):
+        res["outputs"] = [ret[r][2] for r in range(world)]       # [rank][step] -> numpy [B, S_loc, H, D]
+    return res

@@ -22,3 +22,41 @@ def test_reference_arm_under_a_launcher_environment():
             "print('ok')\n" % ROOT)
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "ditango", "core", "attention.py")),
+                    reason="the copy of the reference's attention path has not been made (oracle/make_ref.py)")
+@pytest.mark.parametrize("world,seed", [(4, 0), (4, 1), (8, 2)])
+def test_oracle_equals_the_executed_reference_on_random_legal_schedules(world, seed):
+    """Beyond the committed fixtures: the reference's own proAttention.attn, run here on gloo ranks, against the
+    oracle on fresh random schedules (legalised and screened) and inputs; fp32 on both sides."""
+    import numpy as np
+    import torch
+    from oracle import ref_runner as R
+    from oracle import ring_oracle as O
+    from ditango_b200.core import redundancy_map as rmod
+    from ditango_b200.core.config import init_config
+    rng = np.random.RandomState(seed)
+    T = 8
+    legal = [d for d in (2, 4, 8) if d <= world]
+    div = np.ones((T, 1), dtype=np.int64)
+    for t in range(1, T):
+        if rng.rand() < 0.7:
+            div[t, 0] = legal[rng.randint(len(legal))]
+    cfg = init_config(None, make_output_dir=False)
+    cfg.num_layers, cfg.num_inference_steps = 1, T
+    rmod.destroy_redundancy_map()
+    rm = rmod.init_redundancy_map(cfg, world_size=world)
+    rm.divider_map = torch.from_numpy(div)
+    rm._refine_divider_map()
+    rm.screen_self_sends()
+    col = [int(x) for x in rm.get_map()[:, 0].tolist()]
+    rmod.destroy_redundancy_map()
+    B, S, H, D = 1, 16 * world, 2, 32
+    data = O.drifting_qkv(B, S, H, D, T, seed=10 + seed, drift=0.05)
+    got = R.time_reference(world, dict(B=B, S=S, H=H, D=D, dividers=col, bf16=False, data=data, collect=True), limit_s=240)
+    want, _ = O.run_ring_group(world, col, data)
+    for r in range(world):
+        for t in range(T):
+            err = np.abs(got["outputs"][r][t] - want[t][r].numpy()).max()
+            assert err <= 2e-5, (col, r, t, err)
