@@ -36,6 +36,23 @@ def _cpu_flash(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, return_
     return (o, lse, None) if return_attn_probs else o
 
 
+def _cpu_flash_varlen(q, k, v, cu_q, cu_k, max_q, max_k, dropout_p=0.0, softmax_scale=None, causal=False,
+                      return_attn_probs=False, **kw):
+    """Packed counterpart of _cpu_flash: segment i of q against segment i of k; rows of an empty pairing keep
+    out = 0, lse = -inf."""
+    T, H, _ = q.shape
+    out = torch.zeros_like(q)
+    lse = torch.full((H, T), float("-inf"))
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    for i in range(len(cq) - 1):
+        if cq[i + 1] > cq[i] and ck[i + 1] > ck[i]:
+            o, l, _ = _cpu_flash(q[None, cq[i]:cq[i + 1]], k[None, ck[i]:ck[i + 1]], v[None, ck[i]:ck[i + 1]],
+                                 softmax_scale=softmax_scale, return_attn_probs=True)
+            out[cq[i]:cq[i + 1]] = o[0]
+            lse[:, cq[i]:cq[i + 1]] = l[0]
+    return (out, lse, None) if return_attn_probs else out
+
+
 def _worker(rank, world, case, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
                       RANK=str(rank), LOCAL_RANK=str(rank))
@@ -53,6 +70,7 @@ def _worker(rank, world, case, port, ret):
 
     import ditango.core.attention as A
     A.flash_attn_func = _cpu_flash
+    A.flash_attn_varlen_func = _cpu_flash_varlen
     from ditango.core import parallel_state as ps
     from ditango.core.config import init_config
     from ditango.core.redundancy_map import get_redundancy_map, init_redundancy_map
@@ -91,7 +109,12 @@ def _worker(rank, world, case, port, ret):
         update_timestep(t)
         dist.barrier()
         t0 = time.perf_counter()
-        o = layer.attn(*args)
+        if case.get("cu") is not None:       # packed: this rank's segment table, batch of one
+            cu = torch.tensor(case["cu"][rank], dtype=torch.int32)
+            o = layer.varlen_attn(args[0][0], args[1][0], args[2][0], cu_seqlens_q=cu, cu_seqlens_kv=cu,
+                                  max_seqlen_q=lo, max_seqlen_kv=lo, batch_size=1)[None]
+        else:
+            o = layer.attn(*args)
         dist.barrier()
         seconds += time.perf_counter() - t0
         if outs is not None:

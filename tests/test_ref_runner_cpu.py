@@ -60,3 +60,27 @@ def test_oracle_equals_the_executed_reference_on_random_legal_schedules(world, s
         for t in range(T):
             err = np.abs(got["outputs"][r][t] - want[t][r].numpy()).max()
             assert err <= 2e-5, (col, r, t, err)
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "ditango", "core", "attention.py")),
+                    reason="the copy of the reference's attention path has not been made (oracle/make_ref.py)")
+def test_oracle_equals_the_executed_reference_on_a_packed_batch():
+    """The packed path (varlen_attn) live: four ranks, each with a valid and a pad segment of its own, dividers
+    through a reuse phase; compared on the valid rows (a pad row that meets an empty key segment is undefined in
+    the reference)."""
+    import numpy as np
+    from oracle import ref_runner as R
+    from oracle import ring_oracle as O
+    world, col = 4, [1, 1, 2, 2, 1, 4, 4, 1]
+    B, S, H, D = 1, 24 * world, 2, 32
+    lo = S // world
+    cu = [[0, lo - 5, lo], [0, lo - 9, lo], [0, lo, lo], [0, lo - 3, lo]]
+    data = O.drifting_qkv(B, S, H, D, len(col), seed=21, drift=0.05)
+    got = R.time_reference(world, dict(B=B, S=S, H=H, D=D, dividers=col, bf16=False, data=data, collect=True, cu=cu),
+                           limit_s=240)
+    want, _ = O.run_ring_group(world, col, data, cu_per_rank=cu)
+    for r in range(world):
+        valid = cu[r][1]
+        for t in range(len(col)):
+            err = np.abs(got["outputs"][r][t][0, :valid] - want[t][r][:valid].numpy()).max()
+            assert err <= 2e-5, (r, t, err)
